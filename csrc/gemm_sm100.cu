@@ -1,0 +1,427 @@
+// bf16 GEMM for sm_100a:  C[M,N] = A[M,K] * W[N,K]^T  with fused epilogues.
+//
+// Both operands are K-major (activations row-major, weights in nn.Linear layout), so a tile
+// is a stack of 128-byte rows that TMA drops into shared memory with the 128-byte swizzle and
+// tcgen05.mma consumes through shared-memory descriptors.  One CTA owns a 128 x BN output
+// tile; the fp32 accumulator lives in tensor memory (BN columns x 128 lanes).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (one
+// elected lane issues tcgen05.mma), warps 2..5 = epilogue, each reading the TMEM lane
+// quadrant (warp_id % 4) it is allowed to touch.
+//
+// The decode-time shapes are skinny (M <= 128 rows against 4096..151936 weight rows), i.e.
+// bound by streaming the weights from HBM.  To put all 148 SMs to work on the narrow
+// projections the K dimension can be split across a thread-block cluster (1,1,SPLIT): each
+// CTA accumulates its K range, parks the partial tile in its own shared memory, and after a
+// cluster barrier every CTA reduces and finishes a column slice of the tile by reading its
+// peers' partials through distributed shared memory — no global round trip, no atomics,
+// deterministic summation order.
+//
+// Epilogues: plain store (+ residual), SwiGLU (the tile holds BN/2 gate and BN/2 up columns
+// of the same outputs), per-tile argmax partials (LM head), per-tile top-8 + log-sum-exp
+// partials (draft head logits).
+#include "common.cuh"
+
+#include <math.h>
+
+namespace js {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kTopK = 8;
+
+enum GemmEpi : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_TOPK = 3, EPI_STORE_F32 = 4 };
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;                      // elements
+  void* C;                      // bf16 (or fp32 for EPI_STORE_F32) output
+  const __nv_bfloat16* residual;  // optional, same shape/ld as C (may alias C)
+  float* part_val;              // ARGMAX: [M, n_tiles] ; TOPK: [M, n_tiles, 8] values
+  int* part_idx;                // ARGMAX: [M, n_tiles] ; TOPK: [M, n_tiles, 8] indices
+  float* part_lse;              // TOPK: [M, n_tiles, 2] (running max, sum of exp)
+  int* status;
+};
+
+// BUDGET_KB bounds the pipeline's shared memory: ~96 KB lets two CTAs share an SM (more tiles
+// in flight, natural load balance when the tile count is not a multiple of 148), ~192 KB gives
+// one CTA per SM a deeper pipeline.
+template <int BN, int BUDGET_KB>
+struct GemmSmem {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageW = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageW;
+  static constexpr int kBudget = BUDGET_KB * 1024;
+  static constexpr int kStages = (kBudget / kStage) > 8 ? 8 : ((kBudget / kStage) < 2 ? 2 : (kBudget / kStage));
+  static constexpr int kMinBlocks = BUDGET_KB <= 100 ? 2 : 1;
+  static constexpr int kTiles = kStages * kStage;
+  static constexpr int kRed = BN * BM * 4;   // split-K partial tile, column-major fp32
+  static constexpr int kData = kTiles > kRed ? kTiles : kRed;
+  static constexpr int kBytes = kData + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI, int BUDGET_KB>
+__global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB>::kMinBlocks)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, GemmParams p) {
+  using S = GemmSmem<BN, BUDGET_KB>;
+  constexpr int kStages = S::kStages;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;   // power of two for BN in {32,64,128,256}
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kData);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* accum_bar = empty_bar + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int split = gridDim.z;
+  const int z = blockIdx.z;                  // == rank in the (1,1,split) cluster
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * BM;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = (kb_total * z) / split;
+  const int kb_end = (kb_total * (z + 1)) / split;
+  const int nkb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmW);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Let the next kernel in the stream start its own prologue; it still waits for this grid
+  // to finish before touching our output.
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Weights do not depend on the previous kernel: start streaming them before waiting on it.
+      const int pre = nkb < kStages ? nkb : kStages;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], S::kStage);
+        tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * S::kStage, &tmA, &full_bar[i], (kb_begin + i) * BK, m0);
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) break;
+        mbar_expect_tx(&full_bar[s], S::kStage);
+        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * BK, n0);
+        tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * BK, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % kStages;
+        const uint32_t ph = (i / kStages) & 1;
+        ok = mbar_wait(&full_bar[s], ph, p.status, kTimeoutFull);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage));
+        const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage + S::kStageA));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // advancing K by 16 elements = 32 bytes inside the swizzle row = +2 in 16-byte units
+          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+      }
+      umma_commit(accum_bar);         // accumulator complete (also releases the epilogue on error)
+    }
+  }
+
+  // ------------------------------------------------------------------ epilogue
+  const bool epi_warp = warp >= 2;
+  const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
+  const int row = quad * 32 + lane;              // row of the tile owned by this thread
+  const int grow = m0 + row;
+  const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+  float* red = reinterpret_cast<float*>(smem);   // [BN][128] column-major partial (split-K only)
+  bool acc_ok = true;
+
+  if (epi_warp) {
+    pdl_wait();   // residual / C may be produced by the previous kernel
+    acc_ok = mbar_wait(accum_bar, 0, p.status, kTimeoutAccum);
+    tc_fence_after();
+  }
+
+  if (split > 1) {
+    // park the partial tile in shared memory (the pipeline stages are idle now)
+    if (epi_warp && acc_ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) red[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+  }
+
+  if (epi_warp && acc_ok) {
+    const uint32_t red_addr = smem_u32(red);
+    // fetch 32 consecutive accumulator columns of this thread's row, reduced over the K split
+    auto load_chunk = [&](int c0, float* v) {
+      if (split == 1) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        for (int pr = 0; pr < split; ++pr) {
+          const uint32_t base = map_to_cta(red_addr, pr) + (c0 * BM + row) * 4;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += ld_dsmem_f32(base + j * BM * 4);
+        }
+      }
+    };
+
+    if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
+      // 32-column chunks are dealt round-robin to the CTAs of the K-split cluster
+      for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
+        float v[32];
+        load_chunk(c0, v);
+        const int gc = n0 + c0;
+        if (grow < p.M && gc < p.N) {
+          if constexpr (EPI == EPI_STORE_F32) {
+            float* out = reinterpret_cast<float*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (gc + j < p.N) *reinterpret_cast<float4*>(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
+            const __nv_bfloat16* res = p.residual ? p.residual + static_cast<size_t>(grow) * p.ldc + gc : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (gc + j >= p.N) break;
+              if (res) {
+                uint4 rv = *reinterpret_cast<const uint4*>(res + j);
+                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  float2 f = __bfloat1622float2(r2[t]);
+                  v[j + 2 * t] += f.x;
+                  v[j + 2 * t + 1] += f.y;
+                }
+              }
+              uint4 ov;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) o2[t] = __floats2bfloat162_rn(v[j + 2 * t], v[j + 2 * t + 1]);
+              *reinterpret_cast<uint4*>(out + j) = ov;
+            }
+          }
+        }
+      }
+    } else if constexpr (EPI == EPI_SWIGLU) {
+      constexpr int HALF = BN / 2;
+      for (int c0 = z * 32; c0 < HALF; c0 += split * 32) {
+        float g[32], u[32];
+        load_chunk(c0, g);
+        load_chunk(HALF + c0, u);
+        const int gc = n0 / 2 + c0;              // output column
+        if (grow < p.M && gc < p.N / 2) {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 ov;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float a = g[j + 2 * t], b = g[j + 2 * t + 1];
+              o2[t] = __floats2bfloat162_rn(a / (1.f + __expf(-a)) * u[j + 2 * t], b / (1.f + __expf(-b)) * u[j + 2 * t + 1]);
+            }
+            *reinterpret_cast<uint4*>(out + j) = ov;
+          }
+        }
+      }
+    } else if constexpr (EPI == EPI_ARGMAX) {
+      float best = -INFINITY;
+      int best_i = 0x7fffffff;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        load_chunk(c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int gc = n0 + c0 + j;
+          // the values feed an argmax over bf16-rounded logits, like the unfused reference
+          const float x = __bfloat162float(__float2bfloat16_rn(v[j]));
+          if (gc < p.N && x > best) { best = x; best_i = gc; }
+        }
+      }
+      if (grow < p.M) {
+        const size_t o = static_cast<size_t>(grow) * gridDim.x + blockIdx.x;
+        p.part_val[o] = best;
+        p.part_idx[o] = best_i;
+      }
+    } else {  // EPI_TOPK: top-8 values + indices and (max, sum exp) over this tile's columns
+      float tv[kTopK];
+      int ti[kTopK];
+#pragma unroll
+      for (int t = 0; t < kTopK; ++t) { tv[t] = -INFINITY; ti[t] = 0x7fffffff; }
+      float mx = -INFINITY, se = 0.f;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        load_chunk(c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int gc = n0 + c0 + j;
+          if (gc >= p.N) continue;
+          const float x = v[j];
+          if (x > mx) { se = se * __expf(mx - x) + 1.f; mx = x; } else { se += __expf(x - mx); }
+          if (x > tv[kTopK - 1]) {
+            // insertion into the sorted list (descending; ties keep the lower index first)
+            float cv = x; int ci = gc;
+#pragma unroll
+            for (int t = 0; t < kTopK; ++t) {
+              if (cv > tv[t]) { const float sv = tv[t]; const int si = ti[t]; tv[t] = cv; ti[t] = ci; cv = sv; ci = si; }
+            }
+          }
+        }
+      }
+      if (grow < p.M) {
+        const size_t o = static_cast<size_t>(grow) * gridDim.x + blockIdx.x;
+#pragma unroll
+        for (int t = 0; t < kTopK; ++t) { p.part_val[o * kTopK + t] = tv[t]; p.part_idx[o * kTopK + t] = ti[t]; }
+        p.part_lse[o * 2] = mx;
+        p.part_lse[o * 2 + 1] = se;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (split > 1) cluster_sync();   // peers may still be reading this CTA's partial tile
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements), box = [box_rows, 64]
+static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BN, int EPI, int BUDGET_KB>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
+                       cudaStream_t stream) {
+  using S = GemmSmem<BN, BUDGET_KB>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess) return -3;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  attrs[na].id = cudaLaunchAttributeClusterDimension;
+  attrs[na].val.clusterDim.x = 1;
+  attrs[na].val.clusterDim.y = 1;
+  attrs[na].val.clusterDim.z = split;
+  ++na;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tw, p) == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace js
+
+// C = A[M,K] * W[N,K]^T.  epi: 0 store(+residual) 1 swiglu 2 argmax partials 3 top-8 + lse partials 4 fp32 store.
+// bn in {32,64,128,256}; split = K-split cluster size (1..4; store/swiglu only); deep != 0 selects the
+// one-CTA-per-SM deep pipeline instead of the two-CTAs-per-SM one.  Returns 0 or a negative code.
+extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* residual, int M, int N, int K, int lda,
+                            int ldw, int ldc, int epi, int bn, int split, int deep, float* part_val, int* part_idx,
+                            float* part_lse, int* status, int pdl, cudaStream_t stream) {
+  using namespace js;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (lda % 8) || (ldw % 8)) return -10;           // TMA: 16-byte aligned rows
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
+  const int kb_total = (K + BK - 1) / BK;
+  if (split < 1 || split > 8 || split > kb_total) return -12;
+  if ((epi == EPI_ARGMAX || epi == EPI_TOPK) && split != 1) return -13;
+  if (epi == EPI_SWIGLU && split > bn / 64) return -14;
+  if ((epi == EPI_STORE || epi == EPI_STORE_F32) && split > bn / 32) return -14;
+  if ((epi == EPI_STORE || epi == EPI_SWIGLU) && (ldc % 8)) return -15;
+  CUtensorMap ta, tw;
+  if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, bn)) return -16;
+  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status};
+#define JS_CASE(BN_, EPI_)                                                                              \
+  if (bn == BN_ && epi == EPI_)                                                                         \
+    return deep ? launch_gemm<BN_, EPI_, 192>(ta, tw, p, split, pdl != 0, stream)                       \
+                : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
+  JS_CASE(64, EPI_STORE) JS_CASE(128, EPI_STORE) JS_CASE(256, EPI_STORE)
+  JS_CASE(128, EPI_STORE_F32)
+  JS_CASE(128, EPI_SWIGLU) JS_CASE(256, EPI_SWIGLU)
+  JS_CASE(128, EPI_ARGMAX)
+  JS_CASE(128, EPI_TOPK)
+#undef JS_CASE
+  return -17;
+}

@@ -1,0 +1,347 @@
+// Memory-bound helper kernels of the decode round: embedding gather, RMSNorm, the fused
+// QKV post-processing (per-head RMSNorm + RoPE + KV scatter into slots), SwiGLU, row
+// gathers, and the merges of the per-tile argmax / top-k partials the LM-head GEMM emits.
+// All math is fp32; tensors are bf16.  Each kernel joins programmatic dependent launch:
+// it lets its successor start early and waits for its predecessor before reading.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace js {
+
+JS_DEVICE void bf16x8_to_float(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+JS_DEVICE uint4 float_to_bf16x8(const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+// out[t, :] = table[ids[t], :]     (H % 8 == 0)
+__global__ void embed_kernel(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int T, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// y = x * rsqrt(mean(x^2) + eps) * w ; one CTA per row
+__global__ void rmsnorm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* y, int T, int H,
+                               int ldx, int ldy, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * ldx);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    float f[8];
+    bf16x8_to_float(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  __shared__ float red[32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = rsqrtf(v / H + eps);
+  }
+  __syncthreads();
+  const float inv = red[0];
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * ldy);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    float f[8], g[8];
+    bf16x8_to_float(xr[i], f);
+    bf16x8_to_float(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * inv * g[j];
+    yr[i] = float_to_bf16x8(f);
+  }
+}
+
+// Fused QKV post-processing, head_dim 128.  One warp per (token, head) of the fused row
+// [q heads | k heads | v heads]: q and k heads get RMSNorm over the head then rotate-half RoPE
+// at positions[t]; q goes to q_out (T, Hq, 128), k and v go to the pools (Hkv, S, 128) at
+// slots[t].  norm weights may be null (no per-head norm).  q_out may be null (context rows of
+// the draft head only produce K/V).
+__global__ void qkv_post_kernel(const __nv_bfloat16* qkv, int ld, const __nv_bfloat16* qw, const __nv_bfloat16* kw,
+                                const int* positions, const int* slots, const float* inv_freq,
+                                __nv_bfloat16* q_out, __nv_bfloat16* k_pool, __nv_bfloat16* v_pool, int T, int Hq,
+                                int Hkv, int S, float eps, const int* n_valid, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int heads = Hq + 2 * Hkv;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, hd = gw % heads;
+  if (n_valid != nullptr && t >= *n_valid) return;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld + hd * 128;
+  // lane holds elements (2*lane, 2*lane+1) of each half: x1 = [0,64), x2 = [64,128)
+  float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane));
+  float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 64 + 2 * lane));
+  const bool is_q = hd < Hq, is_k = !is_q && hd < Hq + Hkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* nw = is_q ? qw : kw;
+    if (nw != nullptr) {
+      float ss = warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+      const float inv = rsqrtf(ss / 128.f + eps);
+      const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + 2 * lane));
+      const float2 w2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + 64 + 2 * lane));
+      // round to bf16 after the norm, as an unfused norm kernel would
+      a.x = __bfloat162float(__float2bfloat16_rn(a.x * inv * w1.x));
+      a.y = __bfloat162float(__float2bfloat16_rn(a.y * inv * w1.y));
+      b.x = __bfloat162float(__float2bfloat16_rn(b.x * inv * w2.x));
+      b.y = __bfloat162float(__float2bfloat16_rn(b.y * inv * w2.y));
+    }
+    const float pos = static_cast<float>(positions[t]);
+    float s0, c0, s1, c1;
+    sincosf(pos * inv_freq[2 * lane], &s0, &c0);
+    sincosf(pos * inv_freq[2 * lane + 1], &s1, &c1);
+    const float2 ra = make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+    const float2 rb = make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    a = ra;
+    b = rb;
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    if (q_out == nullptr) return;
+    dst = q_out + (static_cast<size_t>(t) * Hq + hd) * 128;
+  } else {
+    int slot = slots[t];
+    if (slot < 0 || slot >= S) {
+      if (lane == 0) report(status, kBadSlot);
+      return;
+    }
+    const int kvh = is_k ? hd - Hq : hd - Hq - Hkv;
+    dst = (is_k ? k_pool : v_pool) + (static_cast<size_t>(kvh) * S + slot) * 128;
+  }
+  *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(a.x, a.y);
+  *reinterpret_cast<__nv_bfloat162*>(dst + 64 + 2 * lane) = __floats2bfloat162_rn(b.x, b.y);
+}
+
+// out[t, j] = silu(in[t, j]) * in[t, I + j]
+__global__ void silu_mul_kernel(const __nv_bfloat16* in, __nv_bfloat16* out, int T, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t n = static_cast<size_t>(T) * I / 8;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / (I / 8), c = i % (I / 8);
+    float g[8], u[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(in + t * 2 * I + c * 8), g);
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(in + t * 2 * I + I + c * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    *reinterpret_cast<uint4*>(out + t * I + c * 8) = float_to_bf16x8(g);
+  }
+}
+
+// dst[i, dst_col0 : dst_col0 + H] = src[idx ? idx[i] : i, :]   (row gather / column-block copy)
+__global__ void gather_rows_kernel(const __nv_bfloat16* src, int lds, const int* idx, const int* n_valid,
+                                   __nv_bfloat16* dst, int ldd, int dst_col0, int rows, int H, int src_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x;
+  if (i >= rows) return;
+  int r = idx != nullptr ? idx[i] : i;
+  const bool valid = (n_valid == nullptr || i < *n_valid) && r >= 0 && r < src_rows;
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(valid ? r : 0) * lds);
+  uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(i) * ldd + dst_col0);
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) d[c] = valid ? s[c] : zero;
+}
+
+// argmax over the per-tile partials of the LM-head GEMM: one warp per row; lowest index wins ties
+__global__ void argmax_merge_kernel(const float* part_val, const int* part_idx, int n_tiles, int M, int* out_idx,
+                                    float* out_val) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lane; i < n_tiles; i += 32) {
+    const float v = part_val[static_cast<size_t>(row) * n_tiles + i];
+    const int ix = part_idx[static_cast<size_t>(row) * n_tiles + i];
+    if (v > best || (v == best && ix < bi)) { best = v; bi = ix; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) {
+    out_idx[row] = bi;
+    if (out_val != nullptr) out_val[row] = best;
+  }
+}
+
+// Merge per-tile top-8 and (max, sum-exp) partials into per-row top-K tokens and full-vocabulary
+// log-probabilities.  One CTA (128 threads) per row.
+__global__ void topk_merge_kernel(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles,
+                                  int M, int K, int* out_tok, float* out_lp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  __shared__ float s_m[128], s_s[128];
+  __shared__ float s_v[128];
+  __shared__ int s_i[128];
+  const int tid = threadIdx.x;
+  // log-sum-exp over tiles
+  float mx = -INFINITY, se = 0.f;
+  for (int i = tid; i < n_tiles; i += blockDim.x) {
+    const float m = part_lse[(static_cast<size_t>(row) * n_tiles + i) * 2];
+    const float s = part_lse[(static_cast<size_t>(row) * n_tiles + i) * 2 + 1];
+    if (m == -INFINITY) continue;
+    if (m > mx) { se = se * __expf(mx - m) + s; mx = m; } else { se += s * __expf(m - mx); }
+  }
+  s_m[tid] = mx;
+  s_s[tid] = se;
+  __syncthreads();
+  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+    if (tid < o) {
+      const float m1 = s_m[tid], m2 = s_m[tid + o];
+      const float m = fmaxf(m1, m2);
+      if (m != -INFINITY) {
+        s_s[tid] = s_s[tid] * __expf(m1 - m) + s_s[tid + o] * __expf(m2 - m);
+        s_m[tid] = m;
+      }
+    }
+    __syncthreads();
+  }
+  const float lse = s_m[0] + logf(s_s[0]);
+  // K rounds of global argmax over the tiles' sorted candidate lists; a candidate emitted in
+  // an earlier round is recognised by its token id and skipped.
+  __shared__ int taken[8];
+  for (int k = 0; k < K; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < n_tiles; i += blockDim.x) {
+      const size_t o = (static_cast<size_t>(row) * n_tiles + i) * 8;
+      for (int e = 0; e < 8; ++e) {
+        const float v = part_val[o + e];
+        const int ix = part_idx[o + e];
+        if (v < bv) break;   // lists are sorted descending
+        bool used = false;
+        for (int q = 0; q < k; ++q) used |= (taken[q] == ix);
+        if (used) continue;
+        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+        break;               // first unused entry of a sorted list is that list's best
+      }
+    }
+    s_v[tid] = bv;
+    s_i[tid] = bi;
+    __syncthreads();
+    for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+      if (tid < o) {
+        const float ov = s_v[tid + o];
+        const int oi = s_i[tid + o];
+        if (ov > s_v[tid] || (ov == s_v[tid] && oi < s_i[tid])) { s_v[tid] = ov; s_i[tid] = oi; }
+      }
+      __syncthreads();
+    }
+    if (tid == 0) {
+      taken[k] = s_i[0];
+      out_tok[row * K + k] = s_i[0];
+      out_lp[row * K + k] = s_v[0] - lse;
+    }
+    __syncthreads();
+  }
+
+}
+
+static cudaLaunchAttribute g_pdl_attr;
+static void launch_cfg(cudaLaunchConfig_t& c, dim3 grid, dim3 block, cudaStream_t stream, int pdl) {
+  c = cudaLaunchConfig_t{};
+  c.gridDim = grid;
+  c.blockDim = block;
+  c.stream = stream;
+  g_pdl_attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  g_pdl_attr.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &g_pdl_attr;
+  c.numAttrs = pdl ? 1 : 0;
+}
+
+}  // namespace js
+
+#define JS_LAUNCH(kern, grid, block, ...)                                             \
+  do {                                                                                \
+    cudaLaunchConfig_t c;                                                             \
+    js::launch_cfg(c, grid, block, stream, pdl);                                      \
+    return cudaLaunchKernelEx(&c, kern, __VA_ARGS__) == cudaSuccess ? 0 : -4;         \
+  } while (0)
+
+extern "C" int js_embed(const int* ids, const void* table, void* out, int T, int H, int V, int pdl, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  JS_LAUNCH(js::embed_kernel, dim3(T), dim3(128), ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, H, V);
+}
+
+extern "C" int js_rmsnorm(const void* x, const void* w, void* y, int T, int H, int ldx, int ldy, float eps, int pdl,
+                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H % 8) || (ldx % 8) || (ldy % 8)) return -10;
+  const int threads = H >= 2048 ? 256 : 128;
+  JS_LAUNCH(js::rmsnorm_kernel, dim3(T), dim3(threads), (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+            (__nv_bfloat16*)y, T, H, ldx, ldy, eps);
+}
+
+extern "C" int js_qkv_post(const void* qkv, int ld, const void* qw, const void* kw, const int* positions,
+                           const int* slots, const float* inv_freq, void* q_out, void* k_pool, void* v_pool, int T,
+                           int Hq, int Hkv, int S, float eps, const int* n_valid, int* status, int pdl,
+                           cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int warps = T * (Hq + 2 * Hkv);
+  JS_LAUNCH(js::qkv_post_kernel, dim3((warps + 7) / 8), dim3(256), (const __nv_bfloat16*)qkv, ld,
+            (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, positions, slots, inv_freq, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, T, Hq, Hkv, S, eps, n_valid, status);
+}
+
+extern "C" int js_silu_mul(const void* in, void* out, int T, int I, int pdl, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I % 8) return -10;
+  const size_t n = static_cast<size_t>(T) * I / 8;
+  const int blocks = static_cast<int>((n + 255) / 256 > 1184 ? 1184 : (n + 255) / 256);
+  JS_LAUNCH(js::silu_mul_kernel, dim3(blocks), dim3(256), (const __nv_bfloat16*)in, (__nv_bfloat16*)out, T, I);
+}
+
+extern "C" int js_gather_rows(const void* src, int lds, const int* idx, const int* n_valid, void* dst, int ldd,
+                              int dst_col0, int rows, int H, int src_rows, int pdl, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((H % 8) || (lds % 8) || (ldd % 8) || (dst_col0 % 8)) return -10;
+  JS_LAUNCH(js::gather_rows_kernel, dim3(rows), dim3(128), (const __nv_bfloat16*)src, lds, idx, n_valid,
+            (__nv_bfloat16*)dst, ldd, dst_col0, rows, H, src_rows);
+}
+
+extern "C" int js_argmax_merge(const float* part_val, const int* part_idx, int n_tiles, int M, int* out_idx,
+                               float* out_val, int pdl, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  JS_LAUNCH(js::argmax_merge_kernel, dim3((M + 7) / 8), dim3(256), part_val, part_idx, n_tiles, M, out_idx, out_val);
+}
+
+extern "C" int js_topk_merge(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles, int M,
+                             int K, int* out_tok, float* out_lp, int pdl, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K < 1 || K > 8) return -10;
+  JS_LAUNCH(js::topk_merge_kernel, dim3(M), dim3(128), part_val, part_idx, part_lse, n_tiles, M, K, out_tok, out_lp);
+}

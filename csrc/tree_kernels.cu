@@ -1,0 +1,315 @@
+// Device-side tree construction and acceptance/commit, so that a whole decode round
+// (draft -> build -> verify -> accept -> commit) replays from one CUDA graph with a single
+// host read at the end.
+//
+// tree_build: best-first expansion under a node budget, bit-identical to the host builder
+// (max-heap on cumulative log-probability held in double, ties broken by insertion order;
+// per-depth fan-out caps; the budget counts the root).  Also emits what the verify forward
+// needs: rotary positions (past + depth), KV slots of the tree window, packed ancestor bits,
+// and pad rows up to the graph's bucket size (token 0, last real position, self-only mask).
+//
+// tree_accept_commit: greedy acceptance (token == target argmax at the parent, the later of
+// two equal siblings wins, deepest fully matching path), then the commit: permute the
+// window's slot-map entries so the accepted nodes' slots become positions past..past+acc,
+// append accepted tokens + correction to the committed-token buffer, advance the sequence
+// state, check EOS, and write a small result record for the host.
+//
+// Reference behaviour: jetspec/tree/_core/fanout_cap_builder.py:18-75, accept.py:73-141,
+// and the no-gather commit at jetspec/inference_engine/engine.py:1114-1125.
+#include "common.cuh"
+
+namespace js {
+
+constexpr int kMaxNodes = 256;
+constexpr int kMaxWords = kMaxNodes / 32;
+
+// sequence state (int32 words) shared by the round's kernels
+enum : int { ST_PAST = 0, ST_CTX = 1, ST_NEW = 2, ST_DONE = 3, ST_GEN = 4, ST_NNODES = 5, ST_ROUNDS = 6 };
+
+struct HeapItem {
+  double key;   // negated cumulative log-probability
+  int order;
+  int node;
+};
+
+JS_DEVICE bool heap_less(const HeapItem& a, const HeapItem& b) {
+  return a.key < b.key || (a.key == b.key && a.order < b.order);
+}
+
+__global__ void __launch_bounds__(256, 1)
+tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget, int NB, int W,
+                  const int* committed, int* state, const int* slot_row, int max_len, int* tokens, int* parents,
+                  int* depth, int* positions, int* slots, int* mask_bits, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ HeapItem heap[kMaxNodes + 1];
+  __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes];
+  __shared__ int s_bits[kMaxNodes][kMaxWords];
+  __shared__ int s_n;
+  const int tid = threadIdx.x;
+  const int past = state[ST_PAST];
+  if (budget > NB) budget = NB;
+
+  if (tid == 0) {
+    int n = 1, hs = 0, order = 0;
+    s_tok[0] = committed[past];
+    s_par[0] = -1;
+    s_dep[0] = 0;
+    for (int w = 0; w < W; ++w) s_bits[0][w] = 0;
+    s_bits[0][0] = 1;
+    heap[hs++] = HeapItem{0.0, 0, 0};
+    while (hs > 0 && n < budget) {
+      // pop min
+      const HeapItem top = heap[0];
+      const HeapItem last = heap[--hs];
+      int i = 0;
+      while (true) {
+        int c = 2 * i + 1;
+        if (c >= hs) break;
+        if (c + 1 < hs && heap_less(heap[c + 1], heap[c])) ++c;
+        if (!heap_less(heap[c], last)) break;
+        heap[i] = heap[c];
+        i = c;
+      }
+      if (hs > 0) heap[i] = last;
+      const int node = top.node;
+      const int d = s_dep[node];
+      if (d >= D) continue;
+      int take = (caps != nullptr) ? caps[d] : K;
+      if (take > K) take = K;
+      if (take > budget - n) take = budget - n;
+      for (int j = 0; j < take; ++j) {
+        const double cum = -top.key + static_cast<double>(topk_lp[d * K + j]);
+        s_tok[n] = topk_tok[d * K + j];
+        s_par[n] = node;
+        s_dep[n] = d + 1;
+        for (int w = 0; w < W; ++w) s_bits[n][w] = s_bits[node][w];
+        s_bits[n][n >> 5] |= (1 << (n & 31));
+        // push
+        HeapItem it{-cum, ++order, n};
+        int h = hs++;
+        while (h > 0) {
+          const int par = (h - 1) >> 1;
+          if (!heap_less(it, heap[par])) break;
+          heap[h] = heap[par];
+          h = par;
+        }
+        heap[h] = it;
+        ++n;
+      }
+    }
+    s_n = n;
+    state[ST_NNODES] = n;
+  }
+  __syncthreads();
+  const int n = s_n;
+  int last_pos = past;
+  for (int i = 0; i < n; ++i) last_pos = max(last_pos, past + s_dep[i]);   // cheap: n <= 256
+  for (int i = tid; i < NB; i += blockDim.x) {
+    const bool real = i < n;
+    tokens[i] = real ? s_tok[i] : 0;
+    parents[i] = real ? s_par[i] : -1;
+    depth[i] = real ? s_dep[i] : 0;
+    positions[i] = real ? past + s_dep[i] : last_pos;
+    const int pos = past + i;
+    if (pos < max_len) {
+      slots[i] = slot_row[pos];
+    } else {
+      slots[i] = 0;
+      report(status, kBadSlot);
+    }
+    for (int w = 0; w < W; ++w) mask_bits[i * W + w] = real ? s_bits[i][w] : ((w == (i >> 5)) ? (1 << (i & 31)) : 0);
+  }
+}
+
+__global__ void __launch_bounds__(256, 1)
+tree_accept_commit_kernel(const int* tokens, const int* parents, const int* depth, const int* greedy, int NB,
+                          int* state, int* slot_row, int max_len, int* committed, int committed_cap,
+                          const int* eos_ids, int n_eos, int max_new, int* path_idx, int* result, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes], s_grd[kMaxNodes], s_ok[kMaxNodes];
+  __shared__ int s_slot[kMaxNodes], s_inpath[kMaxNodes], s_path[kMaxNodes];
+  __shared__ unsigned long long s_best;
+  __shared__ int s_acc;
+  const int tid = threadIdx.x;
+  const int n = state[ST_NNODES];
+  const int past = state[ST_PAST];
+  if (tid == 0) s_best = 0ull;
+  for (int i = tid; i < NB; i += blockDim.x) {
+    s_tok[i] = tokens[i];
+    s_par[i] = parents[i];
+    s_dep[i] = depth[i];
+    s_grd[i] = greedy[i];
+    s_inpath[i] = 0;
+    const int pos = past + i;
+    s_slot[i] = pos < max_len ? slot_row[pos] : 0;
+  }
+  __syncthreads();
+  // per-node match
+  for (int i = tid; i < NB; i += blockDim.x) {
+    int ok = 0;
+    if (i == 0) {
+      ok = 1;
+    } else if (i < n) {
+      const int pr = s_par[i];
+      if (pr >= 0 && pr < n && s_tok[i] == s_grd[pr]) {
+        ok = 1;
+        for (int j = i + 1; j < n; ++j)
+          if (s_par[j] == pr && s_tok[j] == s_tok[i]) { ok = 0; break; }   // a later equal sibling wins
+      }
+    }
+    s_ok[i] = ok;
+  }
+  __syncthreads();
+  // whole root path must match; pick the deepest such node (lowest index on equal depth)
+  for (int i = tid; i < n; i += blockDim.x) {
+    int c = i, good = 1, steps = 0;
+    while (c > 0 && steps <= kMaxNodes) {
+      if (!s_ok[c]) { good = 0; break; }
+      c = s_par[c];
+      if (c < 0 || c >= n) { good = 0; report(status, kBadNode); break; }
+      ++steps;
+    }
+    if (good) {
+      const unsigned long long key = (static_cast<unsigned long long>(s_dep[i] + 1) << 32) |
+                                     static_cast<unsigned long long>(0x7fffffff - i);
+      atomicMax(&s_best, key);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const int best = 0x7fffffff - static_cast<int>(s_best & 0xffffffffull);
+    const int acc = s_dep[best];
+    s_acc = acc;
+    int c = best;
+    for (int d = acc; d >= 0; --d) {
+      s_path[d] = c;
+      s_inpath[c] = 1;
+      c = s_par[c] < 0 ? 0 : s_par[c];
+    }
+    const int corr = s_grd[best];
+    // committed tokens: root is committed[past]; accepted nodes then the correction follow
+    int eos_at = -1;
+    int gen = state[ST_GEN];
+    int emitted = 0;
+    for (int j = 0; j <= acc; ++j) {
+      const int tok = j < acc ? s_tok[s_path[j + 1]] : corr;
+      const int pos = past + 1 + j;
+      if (pos < committed_cap) committed[pos] = tok;
+      result[8 + j] = tok;
+      ++emitted;
+      bool is_eos = false;
+      for (int e = 0; e < n_eos; ++e) is_eos |= (eos_ids[e] == tok);
+      if (is_eos && eos_at < 0) eos_at = j;
+    }
+    gen += emitted;
+    result[0] = acc;
+    result[1] = corr;
+    result[2] = eos_at;
+    result[3] = n;
+    result[4] = past + acc + 1;
+    result[5] = gen;
+    result[6] = atomicAdd(status, 0);
+    for (int j = 0; j <= acc; ++j) path_idx[j] = s_path[j];
+    state[ST_PAST] = past + acc + 1;
+    state[ST_NEW] = acc + 1;
+    state[ST_GEN] = gen;
+    state[ST_ROUNDS] = state[ST_ROUNDS] + 1;
+    if (eos_at >= 0 || gen >= max_new) state[ST_DONE] = 1;
+  }
+  __syncthreads();
+  // slot-map permutation of the window: accepted path first (path order), the rest after
+  const int acc = s_acc;
+  for (int i = tid; i < NB; i += blockDim.x) {
+    int dst;
+    if (s_inpath[i]) {
+      dst = s_dep[i];                 // a path node's order on the path is its depth
+    } else {
+      int before = 0;
+      for (int j = 0; j < i; ++j) before += s_inpath[j] ? 0 : 1;
+      dst = acc + 1 + before;
+    }
+    const int pos = past + dst;
+    if (pos < max_len) slot_row[pos] = s_slot[i];
+  }
+}
+
+// positions / slots / block token ids of one draft-head step.  The block is
+// [anchor, mask, mask, ...]; its rows sit at positions ctx .. ctx+bs-1 where ctx is the
+// context length AFTER this round's new rows (state[ST_CTX] + state[ST_NEW]).
+__global__ void draft_prep_kernel(int* state, const int* committed, int mask_token, int bs, int rows_pad,
+                                  int ctx_rows_pad, int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const int ctx_old = state[ST_CTX];
+  const int n_new = state[ST_NEW];
+  const int ctx = ctx_old + n_new;
+  const int past = state[ST_PAST];
+  for (int i = tid; i < rows_pad; i += blockDim.x) {
+    block_ids[i] = (i == 0) ? committed[past] : mask_token;
+    block_pos[i] = ctx + i;
+  }
+  for (int i = tid; i < ctx_rows_pad; i += blockDim.x) ctx_pos[i] = ctx_old + i;
+  __syncthreads();
+  if (tid == 0) {
+    *n_new_out = n_new;
+    state[ST_CTX] = ctx;
+    state[ST_NEW] = 0;
+  }
+}
+
+}  // namespace js
+
+extern "C" int js_tree_build(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget,
+                             int NB, int W, const int* committed, int* state, const int* slot_row, int max_len,
+                             int* tokens, int* parents, int* depth, int* positions, int* slots, int* mask_bits,
+                             int* status, int pdl, cudaStream_t stream) {
+  if (NB < 1 || NB > js::kMaxNodes || W < 1 || W > js::kMaxWords || NB > W * 32) return -10;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(256);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::tree_build_kernel, topk_tok, topk_lp, caps, D, K, budget, NB, W, committed, state,
+                            slot_row, max_len, tokens, parents, depth, positions, slots, mask_bits, status) == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int js_tree_accept_commit(const int* tokens, const int* parents, const int* depth, const int* greedy,
+                                     int NB, int* state, int* slot_row, int max_len, int* committed, int committed_cap,
+                                     const int* eos_ids, int n_eos, int max_new, int* path_idx, int* result,
+                                     int* status, int pdl, cudaStream_t stream) {
+  if (NB < 1 || NB > js::kMaxNodes) return -10;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(256);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::tree_accept_commit_kernel, tokens, parents, depth, greedy, NB, state, slot_row,
+                            max_len, committed, committed_cap, eos_ids, n_eos, max_new, path_idx, result, status) == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int js_draft_prep(int* state, const int* committed, int mask_token, int bs, int rows_pad, int ctx_rows_pad,
+                             int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out, int pdl,
+                             cudaStream_t stream) {
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(64);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::draft_prep_kernel, state, committed, mask_token, bs, rows_pad, ctx_rows_pad,
+                            block_ids, block_pos, ctx_pos, n_new_out) == cudaSuccess ? 0 : -4;
+}

@@ -22,7 +22,7 @@ def _kern(x: torch.Tensor) -> bool:
 
 def _ext():
     from . import cuda_ext
-    return cuda_ext.load()
+    return cuda_ext
 
 
 def rmsnorm(x, weight, eps: float = 1e-6):
@@ -51,8 +51,15 @@ def silu_mul(gate_up):
 
 def qkv_postprocess(qkv, q_norm_w, k_norm_w, positions, num_q_heads, num_kv_heads, head_dim, theta, eps):
     if _kern(qkv) and head_dim == 128:
-        return _ext().qkv_postprocess(qkv, q_norm_w, k_norm_w, positions.to(torch.int32),
-                                      num_q_heads, num_kv_heads, head_dim, float(theta), float(eps))
+        ext = _ext()
+        T = qkv.shape[0]
+        q = torch.empty(T, num_q_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty(num_kv_heads, T, head_dim, dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+        rows = torch.arange(T, dtype=torch.int32, device=qkv.device)
+        ext.qkv_post(qkv, q_norm_w, k_norm_w, positions.to(torch.int32), rows,
+                     ext.inv_freq(head_dim, theta, qkv.device), q, k, v, num_q_heads, num_kv_heads, float(eps))
+        return q, k.transpose(0, 1), v.transpose(0, 1)
     return ref.qkv_postprocess(qkv, q_norm_w, k_norm_w, positions, num_q_heads, num_kv_heads,
                                head_dim, theta, eps)
 
@@ -64,7 +71,7 @@ def kv_scatter(k, v, k_pool, v_pool, slots):
 def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens, mask_bits, scale,
                          causal: bool = False, max_q: Optional[int] = None):
     if _kern(q) and q.shape[-1] == 128:
-        return _ext().paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
+        return _ext().paged_tree_attention(q.contiguous(), k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
                                            mask_bits, float(scale), bool(causal),
                                            int(max_q if max_q is not None else q.shape[0]))
     return ref.paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,

@@ -1,0 +1,383 @@
+"""Loader and thin tensor-level wrappers for the sm_100a kernel library.
+
+The kernels live in ``csrc/*.cu`` and are compiled by ``nvcc`` for
+``compute_100a/sm_100a`` into one shared library inside the package
+(``jetspec_b200/_C/libjetspec_sm100.so``).  They export plain C entry points that
+take raw device pointers and a stream, so there is no framework ABI to match and
+the library builds in seconds; this module binds them with ``ctypes`` and passes
+``tensor.data_ptr()`` and the current CUDA stream (launches are therefore
+graph-capturable).
+
+On a machine with a GPU a missing or unloadable library is an error, never a
+silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import glob
+import os
+import subprocess
+import sys
+from typing import Optional
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_ROOT = os.path.dirname(_PKG)
+_CSRC = os.path.join(_ROOT, "csrc")
+_OUT_DIR = os.path.join(_PKG, "_C")
+LIB_PATH = os.path.join(_OUT_DIR, "libjetspec_sm100.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-shared"]
+
+_lib = None
+
+
+def sources() -> list:
+    return sorted(glob.glob(os.path.join(_CSRC, "*.cu")))
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = sources() + glob.glob(os.path.join(_CSRC, "*.cuh")) + glob.glob(os.path.join(_CSRC, "*.h"))
+    return any(os.path.getmtime(f) > t for f in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every ``csrc/*.cu`` for sm_100a into the in-tree shared library."""
+    if not force and not _stale():
+        return LIB_PATH
+    if not os.path.isdir(_CSRC):
+        raise RuntimeError(f"kernel sources not found at {_CSRC}")
+    os.makedirs(_OUT_DIR, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + ["-I", _CSRC] + sources() + ["-o", LIB_PATH]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+        print(" ".join(cmd), file=sys.stderr)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(r.stderr, file=sys.stderr)
+    return LIB_PATH
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def load():
+    """``ctypes`` handle of the kernel library (built on first use when a compiler is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if _stale():
+        try:
+            build()
+        except Exception as e:  # no compiler on this machine: use an existing library if there is one
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(f"sm_100a kernel library is missing and could not be built: {e}") from e
+    lib = ctypes.CDLL(LIB_PATH)
+    for name in ("js_gemm_bf16", "js_paged_tree_attention", "js_embed", "js_rmsnorm", "js_qkv_post", "js_silu_mul",
+                 "js_gather_rows", "js_argmax_merge", "js_topk_merge", "js_tree_build", "js_tree_accept_commit",
+                 "js_draft_prep"):
+        getattr(lib, name).restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+# ------------------------------------------------------------------ helpers
+_vp = ctypes.c_void_p
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _vp(t.data_ptr()) if t is not None else _vp(0)
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+_status: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the kernels write an error code to (0 = ok)."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+STATUS_NAMES = {0: "ok", 1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
+                3: "timeout waiting for the accumulator", 4: "timeout waiting for a peer flag",
+                5: "KV slot out of range", 6: "tree node index out of range"}
+
+
+def check_status(device) -> None:
+    """Raise if any kernel recorded an error since the last check (one host sync)."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+_inv_freq: dict = {}
+
+
+def inv_freq(head_dim: int, theta: float, device) -> torch.Tensor:
+    key = (head_dim, float(theta), str(device))
+    if key not in _inv_freq:
+        from .reference import rope_inv_freq
+        _inv_freq[key] = rope_inv_freq(head_dim, theta, device).contiguous()
+    return _inv_freq[key]
+
+
+# ------------------------------------------------------------------ GEMM
+EPI_STORE, EPI_SWIGLU, EPI_ARGMAX, EPI_TOPK, EPI_STORE_F32 = 0, 1, 2, 3, 4
+SM_COUNT = 148
+_DEEP = os.environ.get("JETSPEC_GEMM_DEEP", "0") == "1"
+
+
+def gemm_supported(M: int, N: int, K: int) -> bool:
+    return K % 8 == 0 and N % 8 == 0 and K >= 64
+
+
+def pick_gemm_config(M: int, N: int, K: int, epi: int):
+    """``(bn, split, deep)``: tile width, K-split cluster size, pipeline variant.
+
+    Decode shapes are weight-streaming bound, so the goal is enough CTAs to cover the
+    SMs (two CTAs fit per SM with the shallow pipeline) without re-reading the
+    activations more than necessary.
+    """
+    bn = 128
+    m_tiles = (M + 127) // 128
+    tiles = m_tiles * ((N + bn - 1) // bn)
+    kb = (K + 63) // 64
+    split = 1
+    if epi in (EPI_STORE, EPI_STORE_F32, EPI_SWIGLU):
+        max_split = 4 if epi != EPI_SWIGLU else 2
+        slots = 2 * SM_COUNT
+        while split < max_split and tiles * (split + 1) <= slots and kb // (split + 1) >= 4:
+            split += 1
+    return bn, split, _DEEP
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, epi: int = EPI_STORE, bn: Optional[int] = None,
+         split: Optional[int] = None, deep: Optional[bool] = None, pdl: bool = False,
+         part_val=None, part_idx=None, part_lse=None) -> torch.Tensor:
+    """``out = x @ w.T`` (+ ``residual``) on the tcgen05 kernel.  ``x (M, K)``, ``w (N, K)`` bf16."""
+    lib = load()
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1
+    cb, cs, cd = pick_gemm_config(M, N, K, epi)
+    bn = bn or cb
+    split = split or cs
+    deep = cd if deep is None else deep
+    if out is None:
+        if epi == EPI_SWIGLU:
+            out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=x.device)
+        elif epi == EPI_STORE_F32:
+            out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+        elif epi in (EPI_STORE,):
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    ldc = out.stride(0) if out is not None else 0
+    rc = lib.js_gemm_bf16(_p(x), _p(w), _p(out), _p(residual), M, N, K, x.stride(0), w.stride(0), ldc, epi, bn,
+                          split, int(bool(deep)), _p(part_val), _p(part_idx), _p(part_lse),
+                          _p(status_word(x.device)), int(pdl), _stream())
+    _check(rc, f"js_gemm_bf16(M={M},N={N},K={K},epi={epi},bn={bn},split={split})")
+    return out
+
+
+def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor, bn: int = 128) -> torch.Tensor:
+    """Weight layout for the SwiGLU epilogue: every ``bn``-row tile holds ``bn/2`` gate rows
+    followed by the ``bn/2`` up rows of the same outputs."""
+    I, H = gate_w.shape
+    h = bn // 2
+    assert I % h == 0
+    g = gate_w.view(I // h, h, H)
+    u = up_w.view(I // h, h, H)
+    return torch.cat((g, u), dim=1).reshape(2 * I, H).contiguous()
+
+
+def n_tiles(N: int, bn: int = 128) -> int:
+    return (N + bn - 1) // bn
+
+
+def lm_head_argmax(h: torch.Tensor, w: torch.Tensor, ws: Optional[dict] = None, pdl: bool = False,
+                   out_idx: Optional[torch.Tensor] = None, out_val: Optional[torch.Tensor] = None):
+    """Greedy token per row: vocabulary GEMM with a per-tile argmax epilogue, then a merge.
+    The ``(M, V)`` logits are never written."""
+    lib = load()
+    M, N = h.shape[0], w.shape[0]
+    nt = n_tiles(N)
+    if ws is None:
+        ws = {"val": torch.empty(M, nt, dtype=torch.float32, device=h.device),
+              "idx": torch.empty(M, nt, dtype=torch.int32, device=h.device)}
+    gemm(h, w, out=None, epi=EPI_ARGMAX, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"])
+    if out_idx is None:
+        out_idx = torch.empty(M, dtype=torch.int32, device=h.device)
+    if out_val is None:
+        out_val = torch.empty(M, dtype=torch.float32, device=h.device)
+    _check(lib.js_argmax_merge(_p(ws["val"]), _p(ws["idx"]), nt, M, _p(out_idx), _p(out_val), int(pdl), _stream()),
+           "js_argmax_merge")
+    return out_idx, out_val
+
+
+def lm_head_topk_logprobs(h: torch.Tensor, w: torch.Tensor, k: int, ws: Optional[dict] = None, pdl: bool = False,
+                          out_tok: Optional[torch.Tensor] = None, out_lp: Optional[torch.Tensor] = None):
+    """Per-row top-``k`` tokens with full-vocabulary log-probabilities, without materialising logits."""
+    lib = load()
+    assert 1 <= k <= 8
+    M, N = h.shape[0], w.shape[0]
+    nt = n_tiles(N)
+    if ws is None:
+        ws = {"val": torch.empty(M, nt, 8, dtype=torch.float32, device=h.device),
+              "idx": torch.empty(M, nt, 8, dtype=torch.int32, device=h.device),
+              "lse": torch.empty(M, nt, 2, dtype=torch.float32, device=h.device)}
+    gemm(h, w, out=None, epi=EPI_TOPK, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"],
+         part_lse=ws["lse"])
+    if out_tok is None:
+        out_tok = torch.empty(M, k, dtype=torch.int32, device=h.device)
+    if out_lp is None:
+        out_lp = torch.empty(M, k, dtype=torch.float32, device=h.device)
+    _check(lib.js_topk_merge(_p(ws["val"]), _p(ws["idx"]), _p(ws["lse"]), nt, M, k, _p(out_tok), _p(out_lp),
+                             int(pdl), _stream()), "js_topk_merge")
+    return out_tok, out_lp
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, pdl: bool = False):
+    lib = load()
+    T, (V, H) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    _check(lib.js_embed(_p(ids), _p(table), _p(out), T, H, V, int(pdl), _stream()), "js_embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None, pdl: bool = False):
+    lib = load()
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(x2.shape, dtype=x.dtype, device=x.device)
+    o2 = out.reshape(-1, shp[-1])
+    _check(lib.js_rmsnorm(_p(x2), _p(w), _p(o2), x2.shape[0], shp[-1], x2.stride(0), o2.stride(0),
+                          ctypes.c_float(eps), int(pdl), _stream()), "js_rmsnorm")
+    return out.reshape(shp)
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, pdl: bool = False):
+    lib = load()
+    T, I2 = gate_up.shape
+    gate_up = gate_up.contiguous()
+    if out is None:
+        out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib.js_silu_mul(_p(gate_up), _p(out), T, I2 // 2, int(pdl), _stream()), "js_silu_mul")
+    return out
+
+
+def qkv_post(qkv: torch.Tensor, q_norm_w, k_norm_w, positions: torch.Tensor, slots: torch.Tensor,
+             freq: torch.Tensor, q_out: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
+             Hq: int, Hkv: int, eps: float, n_valid: Optional[torch.Tensor] = None, pdl: bool = False):
+    """Per-head RMSNorm + RoPE on the fused QKV rows; q → ``q_out``, k/v → pools at ``slots``."""
+    lib = load()
+    T = qkv.shape[0]
+    S = k_pool.shape[1]
+    _check(lib.js_qkv_post(_p(qkv), qkv.stride(0), _p(q_norm_w), _p(k_norm_w), _p(positions), _p(slots), _p(freq),
+                           _p(q_out), _p(k_pool), _p(v_pool), T, Hq, Hkv, S, ctypes.c_float(eps), _p(n_valid),
+                           _p(status_word(qkv.device)), int(pdl), _stream()), "js_qkv_post")
+    return q_out
+
+
+def gather_rows(src: torch.Tensor, idx: Optional[torch.Tensor], dst: torch.Tensor, dst_col0: int = 0,
+                n_valid: Optional[torch.Tensor] = None, rows: Optional[int] = None, pdl: bool = False):
+    lib = load()
+    rows = rows if rows is not None else (idx.numel() if idx is not None else src.shape[0])
+    H = src.shape[1]
+    _check(lib.js_gather_rows(_p(src), src.stride(0), _p(idx), _p(n_valid), _p(dst), dst.stride(0), dst_col0, rows, H,
+                              src.shape[0], int(pdl), _stream()), "js_gather_rows")
+    return dst
+
+
+# ------------------------------------------------------------------ attention
+def attn_splits(q_tiles: int, Hkv: int, max_keys: int) -> int:
+    ctas = max(1, q_tiles * Hkv)
+    want = max(1, (2 * SM_COUNT + ctas - 1) // ctas)
+    return max(1, min(want, (max_keys + 255) // 256, 16))
+
+
+def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens, mask_bits, scale: float,
+                         causal: bool, max_q: int, out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
+                         ws: Optional[dict] = None, max_keys: Optional[int] = None, pdl: bool = False):
+    """Ragged paged attention with tree (packed-bit) or causal masking.  See
+    :func:`jetspec_b200.ops.reference.paged_tree_attention` for the contract."""
+    lib = load()
+    T, Hq, D = q.shape
+    assert D == 128
+    Hkv, S = k_pool.shape[0], k_pool.shape[1]
+    B = seq_rows.numel()
+    G = Hq // Hkv
+    if out is None:
+        out = torch.empty(T, Hq * D, dtype=q.dtype, device=q.device)
+    if splits is None:
+        npt = max(1, 64 // G)
+        mk = max_keys if max_keys is not None else slot_map.shape[1]
+        splits = attn_splits((T + npt - 1) // npt, Hkv, mk)
+    ws_o = ws_ml = None
+    if splits > 1:
+        if ws is None:
+            ws = {"o": torch.empty(splits, T, Hq, D, dtype=torch.float32, device=q.device),
+                  "ml": torch.empty(splits, T, Hq, 2, dtype=torch.float32, device=q.device)}
+        ws_o, ws_ml = ws["o"], ws["ml"]
+    W = mask_bits.shape[1] if mask_bits is not None else 0
+    _check(lib.js_paged_tree_attention(_p(q), _p(k_pool), _p(v_pool), _p(slot_map), _p(seq_rows), _p(cu_q),
+                                       _p(past_lens), _p(mask_bits), _p(out), _p(ws_o), _p(ws_ml),
+                                       _p(status_word(q.device)), B, T, Hq, Hkv, S, slot_map.shape[1], W,
+                                       int(bool(causal)), int(splits), ctypes.c_float(scale), int(pdl), _stream()),
+           "js_paged_tree_attention")
+    return out
+
+
+# ------------------------------------------------------------------ MoE (grouped through the dense GEMM)
+def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_logits=None):
+    """Sparse MoE on one GPU: route, sort tokens by expert, run each expert's SwiGLU MLP on its
+    contiguous rows with the tcgen05 GEMM, combine with the routing weights."""
+    from . import reference as ref
+    T, H = x.shape
+    E, I2, _ = w_gate_up.shape
+    if router_logits is None:
+        router_logits = gemm(x, gate_w, epi=EPI_STORE_F32) if gemm_supported(T, E, H) else torch.nn.functional.linear(x, gate_w)
+    wts, idx = ref.moe_route(router_logits, top_k, renorm)
+    flat_e = idx.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    tok = torch.arange(T, device=x.device).repeat_interleave(top_k)[order]
+    counts = torch.bincount(flat_e, minlength=E).tolist()
+    xs = x[tok].contiguous()
+    ys = torch.empty(xs.shape[0], H, dtype=x.dtype, device=x.device)
+    s = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        h = gemm(xs[s:s + c], w_gate_up[e])
+        h = silu_mul(h)
+        gemm(h, w_down[e], out=ys[s:s + c])
+        s += c
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    out.index_add_(0, tok, ys.float() * wts.reshape(-1)[order, None])
+    return out.to(x.dtype)
