@@ -38,10 +38,11 @@ JS_DEVICE bool heap_less(const HeapItem& a, const HeapItem& b) {
 
 __global__ void __launch_bounds__(256, 1)
 tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget, int NB, int W,
-                  const int* committed, int* state, const int* slot_row, int max_len, int* tokens, int* parents,
-                  int* depth, int* positions, int* slots, int* mask_bits, int* status) {
+                  const int* committed, int* state, const int* slot_map, const int* seq_row, int max_len,
+                  int* tokens, int* parents, int* depth, int* positions, int* slots, int* mask_bits, int* status) {
   pdl_launch_dependents();
   pdl_wait();
+  const int* slot_row = slot_map + static_cast<size_t>(*seq_row) * max_len;
   __shared__ HeapItem heap[kMaxNodes + 1];
   __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes];
   __shared__ int s_bits[kMaxNodes][kMaxWords];
@@ -124,10 +125,12 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
 
 __global__ void __launch_bounds__(256, 1)
 tree_accept_commit_kernel(const int* tokens, const int* parents, const int* depth, const int* greedy, int NB,
-                          int* state, int* slot_row, int max_len, int* committed, int committed_cap,
-                          const int* eos_ids, int n_eos, int max_new, int* path_idx, int* result, int* status) {
+                          int* state, int* slot_map, const int* seq_row, int max_len, int* committed,
+                          int committed_cap, const int* eos_ids, int n_eos, int max_new, int* path_idx, int* result,
+                          int* status) {
   pdl_launch_dependents();
   pdl_wait();
+  int* slot_row = slot_map + static_cast<size_t>(*seq_row) * max_len;
   __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes], s_grd[kMaxNodes], s_ok[kMaxNodes];
   __shared__ int s_slot[kMaxNodes], s_inpath[kMaxNodes], s_path[kMaxNodes];
   __shared__ unsigned long long s_best;
@@ -263,9 +266,9 @@ __global__ void draft_prep_kernel(int* state, const int* committed, int mask_tok
 }  // namespace js
 
 extern "C" int js_tree_build(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget,
-                             int NB, int W, const int* committed, int* state, const int* slot_row, int max_len,
-                             int* tokens, int* parents, int* depth, int* positions, int* slots, int* mask_bits,
-                             int* status, int pdl, cudaStream_t stream) {
+                             int NB, int W, const int* committed, int* state, const int* slot_map,
+                             const int* seq_row, int max_len, int* tokens, int* parents, int* depth, int* positions,
+                             int* slots, int* mask_bits, int* status, int pdl, cudaStream_t stream) {
   if (NB < 1 || NB > js::kMaxNodes || W < 1 || W > js::kMaxWords || NB > W * 32) return -10;
   cudaLaunchConfig_t c = {};
   c.gridDim = dim3(1);
@@ -277,13 +280,13 @@ extern "C" int js_tree_build(const int* topk_tok, const float* topk_lp, const in
   c.attrs = &a;
   c.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&c, js::tree_build_kernel, topk_tok, topk_lp, caps, D, K, budget, NB, W, committed, state,
-                            slot_row, max_len, tokens, parents, depth, positions, slots, mask_bits, status) == cudaSuccess ? 0 : -4;
+                            slot_map, seq_row, max_len, tokens, parents, depth, positions, slots, mask_bits, status) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int js_tree_accept_commit(const int* tokens, const int* parents, const int* depth, const int* greedy,
-                                     int NB, int* state, int* slot_row, int max_len, int* committed, int committed_cap,
-                                     const int* eos_ids, int n_eos, int max_new, int* path_idx, int* result,
-                                     int* status, int pdl, cudaStream_t stream) {
+                                     int NB, int* state, int* slot_map, const int* seq_row, int max_len,
+                                     int* committed, int committed_cap, const int* eos_ids, int n_eos, int max_new,
+                                     int* path_idx, int* result, int* status, int pdl, cudaStream_t stream) {
   if (NB < 1 || NB > js::kMaxNodes) return -10;
   cudaLaunchConfig_t c = {};
   c.gridDim = dim3(1);
@@ -294,8 +297,9 @@ extern "C" int js_tree_accept_commit(const int* tokens, const int* parents, cons
   a.val.programmaticStreamSerializationAllowed = 1;
   c.attrs = &a;
   c.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&c, js::tree_accept_commit_kernel, tokens, parents, depth, greedy, NB, state, slot_row,
-                            max_len, committed, committed_cap, eos_ids, n_eos, max_new, path_idx, result, status) == cudaSuccess ? 0 : -4;
+  return cudaLaunchKernelEx(&c, js::tree_accept_commit_kernel, tokens, parents, depth, greedy, NB, state, slot_map,
+                            seq_row, max_len, committed, committed_cap, eos_ids, n_eos, max_new, path_idx, result,
+                            status) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int js_draft_prep(int* state, const int* committed, int mask_token, int bs, int rows_pad, int ctx_rows_pad,

@@ -126,6 +126,9 @@ class JetSpecEngine:
         want_pages = (tokens_needed + self.block_size - 1) // self.block_size + seqs
         if self._num_pages is not None:
             want_pages = int(self._num_pages)      # an explicit size is a hard size
+        elif self.use_kernels:
+            # captured graphs pin the pool: size it once for a full-length sequence
+            want_pages = max(want_pages, (self._max_seq_len + self.block_size - 1) // self.block_size + seqs)
         max_len = max(self._max_seq_len, int(math.ceil(tokens_needed / max(1, seqs))) + self.block_size)
         if self.pool is not None:
             fits = self.pool.num_pages >= want_pages and self.pool.max_seq_len >= max_len \

@@ -1,0 +1,441 @@
+"""Kernel path of the engine: a whole decode round replayed from one CUDA graph.
+
+A round is ``draft-head step → tree build → verify forward → accept → commit``.  On a
+B200 with bf16 weights every step is a hand-written sm_100a kernel launched with
+programmatic dependent launch, all captured once per tree bucket; the host stages
+at most a few hundred bytes (scripted drafter candidates / fan-out caps), replays
+the graph and reads one small result record — one host synchronisation per round,
+as in the reference's production path (``jetspec/inference_engine/engine.py:881-1164``)
+but with the drafter, the tree builder and the commit inside the same graph.
+
+Per-sequence device state (int32 words, see ``csrc/tree_kernels.cu``):
+``[past, draft_ctx, new_ctx_rows, done, generated, n_nodes, rounds]``.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..core.llm import decode_text
+from ..drafters.head import DraftHeadTreeDrafter
+from ..drafters.oracle import OracleOverrideDrafter, OracleTreeDrafter
+from ..models.qwen3 import MLP
+from ..ops import cuda_ext as X
+from ..ops import reference as ref
+from ..sampling import SamplingParams, sample
+from ..tree.builder import topk_rows
+
+ST_PAST, ST_CTX, ST_NEW, ST_DONE, ST_GEN, ST_NNODES, ST_ROUNDS = range(7)
+_PDL = os.environ.get("JETSPEC_PDL", "1") != "0"
+
+
+def _i32(n, device, fill=0):
+    return torch.full((n,), fill, dtype=torch.int32, device=device)
+
+
+def kernel_layer_weights(layers) -> list:
+    """Kernel-ready per-layer weights: fused QKV (and K|V alone), tile-interleaved gate/up."""
+    out = []
+    for layer in layers:
+        if not isinstance(layer.mlp, MLP):
+            raise NotImplementedError("the graph path covers dense MLP layers")
+        a = layer.self_attn
+        if a.q_proj.bias is not None:
+            raise NotImplementedError("the graph path covers bias-free attention projections")
+        out.append({
+            "ln1": layer.input_layernorm.weight, "ln2": layer.post_attention_layernorm.weight,
+            "qkv": torch.cat((a.q_proj.weight, a.k_proj.weight, a.v_proj.weight), 0).contiguous(),
+            "kv": torch.cat((a.k_proj.weight, a.v_proj.weight), 0).contiguous(),
+            "qn": a.q_norm.weight, "kn": a.k_norm.weight, "o": a.o_proj.weight,
+            "gu": X.interleave_gate_up(layer.mlp.gate_proj.weight, layer.mlp.up_proj.weight, 128),
+            "down": layer.mlp.down_proj.weight,
+        })
+    return out
+
+
+class _Stack:
+    """Static activation buffers of one decoder stack for a fixed row count ``T``."""
+
+    def __init__(self, cfg, T: int, device, max_keys: int):
+        H, I = cfg.hidden_size, cfg.intermediate_size
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        bf = dict(dtype=torch.bfloat16, device=device)
+        self.T = T
+        self.x = torch.zeros(T, H, **bf)
+        self.h = torch.zeros(T, H, **bf)
+        self.qkv = torch.zeros(T, (Hq + 2 * Hkv) * D, **bf)
+        self.q = torch.zeros(T, Hq, D, **bf)
+        self.attn = torch.zeros(T, Hq * D, **bf)
+        self.act = torch.zeros(T, I, **bf)
+        npt = max(1, 64 // (Hq // Hkv))
+        self.splits = X.attn_splits((T + npt - 1) // npt, Hkv, max_keys)
+        self.attn_ws = None
+        if self.splits > 1:
+            self.attn_ws = {"o": torch.zeros(self.splits, T, Hq, D, dtype=torch.float32, device=device),
+                            "ml": torch.zeros(self.splits, T, Hq, 2, dtype=torch.float32, device=device)}
+
+
+def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
+                   mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True) -> int:
+    """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count."""
+    Hq, Hkv, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
+    scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
+    last = len(layers) - 1
+    n = 0
+    for li, L in enumerate(layers):
+        X.rmsnorm(st.x, L["ln1"], eps, out=st.h, pdl=pdl)
+        X.gemm(st.h, L["qkv"], out=st.qkv, pdl=pdl)
+        X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps, pdl=pdl)
+        X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits, scale,
+                               causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
+        X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
+        X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
+        X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
+        X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
+        n += 8 + (1 if st.splits > 1 else 0)
+        if taps is not None and li in tap_ids and li != last:
+            X.gather_rows(st.x, None, taps, dst_col0=tap_ids.index(li) * H, pdl=pdl)
+            n += 1
+    return n
+
+
+class FastRound:
+    """Graph-captured decode rounds for one engine (single sequence, greedy)."""
+
+    @classmethod
+    def get(cls, engine) -> "FastRound":
+        if engine._fast is None:
+            engine._fast = cls(engine)
+        return engine._fast
+
+    def __init__(self, engine):
+        self.eng = engine
+        self.cfg = engine.cfg
+        self.device = torch.device(engine.device)
+        X.load()
+        m = engine.model
+        self.embed_w, self.lm_head_w, self.final_norm = m.model.embed_tokens.weight, m.lm_head.weight, m.model.norm.weight
+        self.layers = kernel_layer_weights(m.model.layers)
+        self.freq = X.inv_freq(self.cfg.head_dim, self.cfg.rope_theta, self.device)
+        self.graphs: dict = {}
+        self.draft_cache: dict = {}
+        self.launches_per_round = 0
+
+    # ------------------------------------------------------------------ support matrix
+    def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget) -> bool:
+        cfg = self.cfg
+        if cfg.head_dim != 128 or cfg.is_moe or budget > 256 or tree_width > 8 or block_size - 1 > 48:
+            return False
+        return hasattr(algo_obj, "caps_from_topk")
+
+    @staticmethod
+    def _split_drafter(drafter):
+        """``(head drafter | None, oracle | None, host drafter | None)``."""
+        if isinstance(drafter, OracleOverrideDrafter):
+            real = drafter.real if isinstance(drafter.real, DraftHeadTreeDrafter) else None
+            return real, drafter.oracle, (None if real is not None else drafter.real)
+        if isinstance(drafter, OracleTreeDrafter):
+            return None, drafter, None
+        if isinstance(drafter, DraftHeadTreeDrafter):
+            return drafter, None, None
+        return None, None, drafter
+
+    # ------------------------------------------------------------------ buffers + capture
+    def _round(self, NB: int, D: int, K: int, budget: int, head: Optional[DraftHeadTreeDrafter], staged: bool,
+               tap_ids, max_new: int):
+        pool = self.eng.pool
+        tap_ids = list(tap_ids) if (tap_ids and head is not None) else None
+        key = (NB, D, K, budget, id(head) if head is not None else 0, staged, tuple(tap_ids or ()), id(pool))
+        if key in self.graphs:
+            return self.graphs[key]
+        if pool.resident():
+            raise RuntimeError("a decode graph must be captured before any sequence is resident in the pool")
+        cfg, dev = self.cfg, self.device
+        H = cfg.hidden_size
+        words = max(1, (NB + 31) // 32)
+        Dn, Kn = max(1, D), max(1, K)
+        r = {"NB": NB, "D": D, "K": K, "W": words, "budget": budget, "head": head, "staged": staged,
+             "max_new": 1 << 30, "tap_ids": tap_ids}
+        r["state"] = _i32(8, dev)
+        r["committed"] = _i32(pool.max_seq_len + 64, dev)
+        for name in ("tokens", "parents", "depth", "positions", "slots", "greedy"):
+            r[name] = _i32(NB, dev)
+        r["mask"] = _i32(NB * words, dev).view(NB, words)
+        r["topk_tok"] = _i32(Dn * Kn, dev).view(Dn, Kn)
+        r["topk_lp"] = torch.zeros(Dn, Kn, dtype=torch.float32, device=dev)
+        r["caps"] = _i32(Dn, dev, fill=K)
+        r["path_idx"] = _i32(64, dev)
+        r["result"] = _i32(64, dev)
+        r["result_host"] = torch.zeros(64, dtype=torch.int32).pin_memory()
+        r["stage_tok"] = torch.zeros(Dn, Kn, dtype=torch.int32).pin_memory()
+        r["stage_lp"] = torch.zeros(Dn, Kn, dtype=torch.float32).pin_memory()
+        r["stage_caps"] = torch.full((Dn,), K, dtype=torch.int32).pin_memory()
+        r["cu_q"] = torch.tensor([0, NB], dtype=torch.int32, device=dev)
+        r["seq_rows"] = _i32(1, dev)
+        eos = sorted(self.eng.eos_token_ids)
+        r["eos"] = torch.tensor(eos or [-1], dtype=torch.int32, device=dev)
+        r["n_eos"] = len(eos)
+        r["stack"] = _Stack(cfg, NB, dev, pool.max_seq_len)
+        r["xn"] = torch.zeros(NB, H, dtype=torch.bfloat16, device=dev)
+        nt = X.n_tiles(cfg.vocab_size)
+        r["am_ws"] = {"val": torch.zeros(NB, nt, dtype=torch.float32, device=dev),
+                      "idx": torch.zeros(NB, nt, dtype=torch.int32, device=dev)}
+        r["am_val"] = torch.zeros(NB, dtype=torch.float32, device=dev)
+        r["taps"] = torch.zeros(NB, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
+        if head is not None:
+            self._draft_buffers(r, head)
+        # run every kernel once outside capture (module load, function attributes), then capture
+        r["launches"] = self._launch_round(r, pdl=False)
+        torch.cuda.synchronize()
+        X.status_word(dev).zero_()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._launch_round(r, pdl=_PDL)
+        r["graph"] = g
+        pool.frozen = True
+        self.graphs[key] = r
+        self.launches_per_round = r["launches"]
+        return r
+
+    def _draft_buffers(self, r, head: DraftHeadTreeDrafter):
+        dev = self.device
+        hm = head.head
+        hc = hm.config
+        if hm.hidden_dim_adapter is not None:
+            raise NotImplementedError("heads with a hidden_dim_adapter use the eager path")
+        bs = head.block_size
+        cap = self.eng.pool.max_seq_len + 2 * bs + 64
+        dkey = (id(head), cap)
+        if dkey not in self.draft_cache:
+            layers = kernel_layer_weights(hm.layers)
+            Hkv, Dh = hc.num_key_value_heads, hc.head_dim
+            self.draft_cache[dkey] = {
+                "layers": layers,
+                "k": [torch.zeros(Hkv, cap, Dh, dtype=torch.bfloat16, device=dev) for _ in layers],
+                "v": [torch.zeros(Hkv, cap, Dh, dtype=torch.bfloat16, device=dev) for _ in layers],
+                "slot_map": torch.arange(cap, dtype=torch.int32, device=dev).view(1, cap), "cap": cap}
+        d = dict(self.draft_cache[dkey])
+        H, ntap, Dd, K = hc.hidden_size, len(head.target_layer_ids), bs - 1, max(1, r["K"])
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        d["bs"] = bs
+        d["block_ids"], d["block_pos"], d["ctx_pos"], d["n_new"] = _i32(bs, dev), _i32(bs, dev), _i32(bs, dev), _i32(1, dev)
+        d["ctx_in"] = torch.zeros(bs, ntap * H, **bf)
+        d["ctx_h"], d["ctx_n"], d["hn"] = torch.zeros(bs, H, **bf), torch.zeros(bs, H, **bf), torch.zeros(bs, H, **bf)
+        d["kv"] = torch.zeros(bs, 2 * hc.num_key_value_heads * hc.head_dim, **bf)
+        d["stack"] = _Stack(hc, bs, dev, d["cap"])
+        d["cu_q"] = torch.tensor([0, bs], dtype=torch.int32, device=dev)
+        d["seq_rows"] = _i32(1, dev)
+        d["full_mask"] = torch.full((bs, max(1, (bs + 31) // 32)), -1, dtype=torch.int32, device=dev)
+        nt = X.n_tiles(self.cfg.vocab_size)
+        d["tk_ws"] = {"val": torch.zeros(Dd, nt, 8, dtype=torch.float32, device=dev),
+                      "idx": torch.zeros(Dd, nt, 8, dtype=torch.int32, device=dev),
+                      "lse": torch.zeros(Dd, nt, 2, dtype=torch.float32, device=dev)}
+        d["topk_tok"] = _i32(Dd * K, dev).view(Dd, K)
+        d["topk_lp"] = torch.zeros(Dd, K, dtype=torch.float32, device=dev)
+        d["freq"] = X.inv_freq(hc.head_dim, hc.rope_theta, dev)
+        r["draft"] = d
+
+    def _launch_draft(self, r, pdl) -> int:
+        head, d = r["head"], r["draft"]
+        hm, hc = head.head, head.head.config
+        lib, p, s = X.load(), X._p, X._stream
+        bs, eps, Hkv = d["bs"], hc.rms_norm_eps, hc.num_key_value_heads
+        X._check(lib.js_draft_prep(p(r["state"]), p(r["committed"]), int(hm.mask_token_id), bs, bs, bs,
+                                   p(d["block_ids"]), p(d["block_pos"]), p(d["ctx_pos"]), p(d["n_new"]), int(pdl), s()),
+                 "js_draft_prep")
+        # context update: tap rows of the previously accepted path -> fc -> norm -> per-layer K/V
+        X.gather_rows(r["taps"], r["path_idx"], d["ctx_in"], n_valid=d["n_new"], rows=bs, pdl=pdl)
+        X.gemm(d["ctx_in"], hm.fc.weight, out=d["ctx_h"], pdl=pdl)
+        X.rmsnorm(d["ctx_h"], hm.hidden_norm.weight, eps, out=d["ctx_n"], pdl=pdl)
+        n = 4
+        for li, L in enumerate(d["layers"]):
+            X.gemm(d["ctx_n"], L["kv"], out=d["kv"], pdl=pdl)
+            X.qkv_post(d["kv"], None, L["kn"], d["ctx_pos"], d["ctx_pos"], d["freq"], None, d["k"][li], d["v"][li],
+                       0, Hkv, eps, n_valid=d["n_new"], pdl=pdl)
+            n += 2
+        # block forward over [anchor, mask, mask, ...]
+        st = d["stack"]
+        X.embed(d["block_ids"], head._fwd.embed_w, out=st.x, pdl=pdl)
+        causal = hm.resolve_causal_head("auto")
+        n += 1 + decoder_layers(hc, d["layers"], st, d["k"], d["v"], d["slot_map"], d["seq_rows"], d["cu_q"],
+                                r["state"][ST_CTX:ST_CTX + 1], d["block_pos"], d["block_pos"],
+                                None if causal else d["full_mask"], causal, d["freq"], pdl=pdl)
+        X.rmsnorm(st.x, hm.norm.weight, eps, out=d["hn"], pdl=pdl)
+        rows = d["hn"][:bs - 1] if head.draft_shift else d["hn"][1:bs]
+        X.lm_head_topk_logprobs(rows, head._fwd.lm_head_w, max(1, r["K"]), ws=d["tk_ws"], pdl=pdl,
+                                out_tok=d["topk_tok"], out_lp=d["topk_lp"])
+        return n + 3
+
+    def _launch_round(self, r, pdl: bool) -> int:
+        lib, p, s = X.load(), X._p, X._stream
+        pool, cfg = self.eng.pool, self.cfg
+        NB, D, K = r["NB"], r["D"], r["K"]
+        status = X.status_word(self.device)
+        n = 0
+        if r["head"] is not None and D > 0:
+            n += self._launch_draft(r, pdl)
+            if not r["staged"]:
+                r["topk_tok"].copy_(r["draft"]["topk_tok"][:D])
+                r["topk_lp"].copy_(r["draft"]["topk_lp"][:D])
+        if r["staged"] and D > 0:
+            r["topk_tok"].copy_(r["stage_tok"], non_blocking=True)
+            r["topk_lp"].copy_(r["stage_lp"], non_blocking=True)
+            r["caps"].copy_(r["stage_caps"], non_blocking=True)
+        X._check(lib.js_tree_build(p(r["topk_tok"]), p(r["topk_lp"]), p(r["caps"]), D, max(1, K), r["budget"], NB,
+                                   r["W"], p(r["committed"]), p(r["state"]), p(pool.slot_map), p(r["seq_rows"]),
+                                   pool.max_seq_len, p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["positions"]),
+                                   p(r["slots"]), p(r["mask"]), p(status), int(pdl), s()), "js_tree_build")
+        st = r["stack"]
+        X.embed(r["tokens"], self.embed_w, out=st.x, pdl=pdl)
+        n += 2 + decoder_layers(cfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"], r["cu_q"],
+                                r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"], False,
+                                self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl)
+        X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
+        last = cfg.num_hidden_layers - 1
+        if r["taps"] is not None and last in r["tap_ids"]:
+            X.gather_rows(r["xn"], None, r["taps"], dst_col0=r["tap_ids"].index(last) * cfg.hidden_size, pdl=pdl)
+            n += 1
+        X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        X._check(lib.js_tree_accept_commit(p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["greedy"]), NB,
+                                           p(r["state"]), p(pool.slot_map), p(r["seq_rows"]), pool.max_seq_len,
+                                           p(r["committed"]), r["committed"].numel(), p(r["eos"]), r["n_eos"],
+                                           r["max_new"], p(r["path_idx"]), p(r["result"]), p(status), int(pdl), s()),
+                 "js_tree_accept_commit")
+        r["result_host"].copy_(r["result"], non_blocking=True)
+        return n + 4
+
+    # ------------------------------------------------------------------ sequence setup
+    def _begin(self, r, sid: int, ids: torch.Tensor, taps, total: int) -> int:
+        """Prefill through the eager kernel path and initialise the round's device state."""
+        eng, pool = self.eng, self.eng.pool
+        T = ids.shape[1]
+        logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
+        first = int(logits[-1].float().argmax())
+        r["seq_rows"].fill_(pool.state(sid).row)
+        state = torch.zeros(8, dtype=torch.int32)
+        state[ST_PAST], state[ST_GEN] = T, 1
+        committed = torch.zeros(r["committed"].numel(), dtype=torch.int32)
+        committed[:T] = ids[0].to(torch.int32).cpu()
+        committed[T] = first
+        r["committed"].copy_(committed)
+        head = r["head"]
+        if head is not None:
+            d, hm = r["draft"], head.head
+            hc = hm.config
+            n = hidden.shape[0]
+            ctx = hm.project_target_hidden(hidden.to(hm.fc.weight.dtype))
+            cos, sin = ref.rope_cos_sin(torch.arange(n, device=self.device), hc.head_dim, hc.rope_theta)
+            for li, layer in enumerate(hm.layers):
+                a = layer.self_attn
+                k = torch.nn.functional.linear(ctx, a.k_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
+                v = torch.nn.functional.linear(ctx, a.v_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
+                k = ref.apply_rope(ref.rmsnorm(k, a.k_norm.weight, hc.rms_norm_eps), cos, sin)
+                d["k"][li][:, :n] = k.transpose(0, 1)
+                d["v"][li][:, :n] = v.transpose(0, 1)
+            state[ST_CTX] = n
+        r["state"].copy_(state)
+        torch.cuda.synchronize()
+        return first
+
+    # ------------------------------------------------------------------ public entry points
+    @torch.inference_mode()
+    def generate_tree(self, sid, committed, tree_drafter, algo_obj, block_size, tree_width, budget, taps, sp,
+                      return_stats, tree_diag, max_depth, prompt_info, profile_table, total):
+        from .engine import bucket_for_n
+        eng = self.eng
+        D, K, NB = max(1, block_size - 1), int(tree_width), bucket_for_n(budget)
+        head, oracle, host_drafter = self._split_drafter(tree_drafter)
+        staged = oracle is not None or host_drafter is not None
+        logit_free_caps = type(algo_obj).__name__ == "AccumLogP" or getattr(algo_obj, "force_baseline", False)
+        if (host_drafter is not None and taps is not None) or (head is not None and not staged and not logit_free_caps):
+            # a host drafter that conditions on hidden states, or fan-out caps that need the head's
+            # log-probs on the host, take the eager path
+            return eng._generate_tree_eager(sid, committed, tree_drafter, algo_obj, algo_obj.name, None, block_size,
+                                            tree_width, budget, taps, sp, return_stats, prompt_info, profile_table,
+                                            tree_diag, max_depth, None, total)
+        if head is not None:
+            taps = list(head.target_layer_ids) if taps is None else taps
+            if head.block_size != block_size:
+                raise ValueError(f"draft head block_size {head.block_size} != block_size {block_size}")
+        r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens)
+        first = self._begin(r, sid, committed, taps if head is not None else None, total)
+        new_ids = [first]
+        ctx_ids = committed[0].tolist() + [first]
+        accept_lengths, tree_sizes, rounds = [], [], 0
+        depth_hist = [0] * (max_depth + 2) if tree_diag else None
+        done = first in eng.eos_token_ids
+        res = r["result_host"].numpy()
+        stage_tok, stage_lp, stage_caps = r["stage_tok"].numpy(), r["stage_lp"].numpy(), r["stage_caps"].numpy()
+        src = oracle if oracle is not None else host_drafter
+        stream = torch.cuda.current_stream()
+        while len(new_ids) < sp.max_new_tokens and not done:
+            if staged:
+                ctx_t = torch.tensor([ctx_ids], dtype=torch.long, device="cpu" if oracle is not None else eng.device)
+                if hasattr(src, "propose_topk"):
+                    tok, lp = src.propose_topk(ctx_t, D, K)
+                    tok_l, lp_l = tok.tolist(), lp.tolist()
+                else:
+                    tok_l, lp_l = topk_rows(src.propose_logits(ctx_t, D), K)
+                stage_tok[:] = np.asarray(tok_l, dtype=np.int32)
+                stage_lp[:] = np.asarray(lp_l, dtype=np.float32)
+                stage_caps[:] = np.asarray(algo_obj.caps_from_topk(lp_l, K, prompt_info=prompt_info,
+                                                                   profile_table=profile_table), dtype=np.int32)
+            r["graph"].replay()
+            stream.synchronize()
+            rounds += 1
+            acc, n_nodes = int(res[0]), int(res[3])
+            if int(res[6]) != 0:
+                X.check_status(self.device)
+            block = res[8:8 + acc + 1].tolist()
+            accept_lengths.append(acc + 1)
+            tree_sizes.append(n_nodes)
+            if depth_hist is not None:
+                for dpt in r["depth"][:n_nodes].tolist():
+                    depth_hist[dpt] += 1
+            for t in block:
+                new_ids.append(int(t))
+                ctx_ids.append(int(t))
+                if int(t) in eng.eos_token_ids:
+                    done = True
+                    break
+        if rounds:
+            eng.pool.state(sid).length = int(res[4])
+        new_ids = new_ids[: sp.max_new_tokens]
+        out = {"token_ids": new_ids, "text": decode_text(eng.tokenizer, new_ids),
+               "tpf": (len(new_ids) / rounds if rounds else 0.0)}
+        if return_stats:
+            out.update(accept_lengths=accept_lengths, tree_sizes=tree_sizes, rounds=rounds)
+        if depth_hist is not None:
+            out["tree_nodes_per_depth"] = depth_hist
+        return out
+
+    @torch.inference_mode()
+    def generate_ar(self, sid, ids, sp: SamplingParams):
+        """Autoregressive decode = rounds with a one-node tree (budget 1, no drafter)."""
+        eng = self.eng
+        if sp.temperature > 0.0 or self.cfg.head_dim != 128 or self.cfg.is_moe:
+            logits, _ = eng._prefill(sid, ids[0], reserve=sp.max_new_tokens + 1)
+            out = [int(sample(logits[-1], sp.temperature))]
+            while len(out) < sp.max_new_tokens and out[-1] not in eng.eos_token_ids:
+                past = eng.pool.state(sid).length
+                logits, _, _ = eng._forward([sid], [torch.tensor([out[-1]], device=eng.device)], [past])
+                eng.pool.state(sid).length = past + 1
+                out.append(int(sample(logits[-1], sp.temperature)))
+            return {"token_ids": out, "text": decode_text(eng.tokenizer, out)}
+        T = ids.shape[1]
+        r = self._round(1, 0, 1, 1, None, False, None, sp.max_new_tokens)
+        first = self._begin(r, sid, ids, None, T + sp.max_new_tokens + 2)
+        out = [first]
+        res = r["result_host"].numpy()
+        stream = torch.cuda.current_stream()
+        while len(out) < sp.max_new_tokens and out[-1] not in eng.eos_token_ids:
+            r["graph"].replay()
+            stream.synchronize()
+            if int(res[6]) != 0:
+                X.check_status(self.device)
+            out.append(int(res[8]))
+        return {"token_ids": out, "text": decode_text(eng.tokenizer, out)}

@@ -1,0 +1,141 @@
+"""Kernel-path engine gates on a GPU (bf16): graph-captured AR and tree rounds are lossless up to
+bf16 near-ties, the in-graph draft head matches the eager head, sessions reuse the captured graph."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def small():
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    cfg = Qwen3Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128)
+    return Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda")
+
+
+@pytest.fixture(scope="module")
+def engine(small):
+    from jetspec_b200 import JetSpecEngine
+    return JetSpecEngine(small, device="cuda", dtype=torch.bfloat16, max_seq_len=1024)
+
+
+@pytest.fixture(scope="module")
+def prompt():
+    return torch.randint(0, 4096, (1, 48), generator=torch.Generator().manual_seed(0))
+
+
+def teacher_forced_agreement(model, prompt, new_ids):
+    """Fraction of generated tokens equal to the argmax of one fp32 causal forward over prompt+output,
+    and the worst logit shortfall of a disagreeing token (relative to the row's max |logit|)."""
+    from jetspec_b200.core.model_runner import ModelRunner
+    ref = ModelRunner(model.float())
+    try:
+        ids = torch.cat((prompt.to("cuda"), torch.tensor([new_ids], device="cuda")), 1)
+        logits, _, _ = ref.forward(ids)
+    finally:
+        model.bfloat16()
+    T = prompt.shape[1]
+    rows = logits[0, T - 1:T - 1 + len(new_ids)].float()
+    pick = torch.tensor(new_ids, device="cuda")
+    agree = (rows.argmax(-1) == pick)
+    short = (rows.max(-1).values - rows.gather(1, pick[:, None]).squeeze(1)) / rows.abs().max(-1).values
+    return float(agree.float().mean()), float(short.max())
+
+
+def test_graph_ar_is_greedy(engine, small, prompt):
+    from jetspec_b200 import SamplingParams
+    out = engine.generate(prompt, SamplingParams(0.0, 48))["token_ids"]
+    assert len(out) == 48
+    agree, short = teacher_forced_agreement(small, prompt, out)
+    assert agree > 0.9 and short < 0.05
+
+
+@pytest.mark.parametrize("budget,depth,width", [(8, 4, 2), (60, 8, 4), (128, 20, 7)])
+def test_graph_tree_random_drafter_is_lossless(engine, small, prompt, budget, depth, width):
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter
+    out = engine.generate_tree(prompt, RandomTreeDrafter(4096, seed=1), tree_depth=depth, tree_width=width,
+                               budget=budget, sampling_params=SamplingParams(0.0, 40), return_stats=True, tree_diag=True)
+    assert len(out["token_ids"]) == 40 and out["rounds"] == len(out["accept_lengths"])
+    assert all(1 <= n <= budget for n in out["tree_sizes"])
+    agree, short = teacher_forced_agreement(small, prompt, out["token_ids"])
+    assert agree > 0.9 and short < 0.05
+
+
+def test_graph_tree_oracle_accepts_scripted_lengths(engine, small, prompt):
+    from jetspec_b200 import SamplingParams, OracleTreeDrafter
+    sp = SamplingParams(0.0, 64)
+    cont = prompt[0].tolist() + engine.generate(prompt, sp)["token_ids"]
+    oracle = OracleTreeDrafter(cont, 4096, tree_width=4, mean_accept=3.0, max_accept=7, seed=3)
+    out = None
+    for _ in range(4):      # iterate to the verify path's own fixed point (bf16 near-ties)
+        out = engine.generate_tree(prompt, oracle, tree_depth=8, tree_width=4, budget=32, sampling_params=sp,
+                                   return_stats=True)
+        seq = prompt[0].tolist() + out["token_ids"]
+        if seq == oracle.sequence[:len(seq)]:
+            break
+        oracle.set_continuation(seq)
+    assert seq == oracle.sequence[:len(seq)]
+    planned = oracle.planned[:out["rounds"]]
+    # every round but the last (which may run out of scripted continuation) accepts exactly what was scripted
+    assert out["accept_lengths"][:-1] == [a + 1 for a in planned[:-1]]
+    assert out["tpf"] > 2.0
+
+
+def test_in_graph_draft_head_matches_eager_head(engine, small, prompt):
+    from jetspec_b200 import SamplingParams, DraftHeadTreeDrafter
+    from jetspec_b200.models import DraftHeadModel, draft_head_config
+    from jetspec_b200.engine.fast_round import FastRound
+    hcfg = draft_head_config(small.config, num_layers=1, block_size=9, num_taps=3)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+    drafter = DraftHeadTreeDrafter(head, small, block_size=9)
+    out = engine.generate_tree(prompt, drafter, tree_depth=8, tree_width=4, budget=32,
+                               sampling_params=SamplingParams(0.0, 24), return_stats=True)
+    assert len(out["token_ids"]) == 24
+    agree, short = teacher_forced_agreement(small, prompt, out["token_ids"])
+    assert agree > 0.9 and short < 0.05
+    # replay the last draft step eagerly: same context, same tapped hidden states
+    fast = FastRound.get(engine)
+    r = [g for g in fast.graphs.values() if g["head"] is drafter][0]
+    seq = prompt[0].tolist() + out["token_ids"]
+    from jetspec_b200.core.model_runner import ModelRunner
+    runner = ModelRunner(small)
+    # context of the LAST executed round = everything committed before that round
+    n_before = len(seq) - out["accept_lengths"][-1]
+    ctx = torch.tensor([seq[:n_before]], device="cuda")
+    _, _, hidden = runner.forward(ctx[:, :-1], target_layer_ids=drafter.target_layer_ids)
+    drafter.reset_cache()
+    tok, lp = drafter.propose_topk(ctx, 8, 4, target_hidden=hidden)
+    dev_tok, dev_lp = r["draft"]["topk_tok"][:8], r["draft"]["topk_lp"][:8]
+    assert float((tok.int() == dev_tok).float().mean()) > 0.8
+    assert torch.allclose(lp, dev_lp, atol=0.05)
+
+
+def test_session_reuses_graph(engine, prompt):
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter
+    from jetspec_b200.engine.fast_round import FastRound
+    d = RandomTreeDrafter(4096, seed=2)
+    sp = SamplingParams(0.0, 16)
+    engine.end_session()
+    a = engine.generate_tree(prompt, d, tree_depth=4, tree_width=2, budget=8, sampling_params=sp, session=True)
+    n_graphs = len(FastRound.get(engine).graphs)
+    b = engine.generate_tree(prompt, RandomTreeDrafter(4096, seed=2), tree_depth=4, tree_width=2, budget=8,
+                             sampling_params=sp, session=True)
+    assert len(FastRound.get(engine).graphs) == n_graphs      # captured once, replayed after
+    assert a["token_ids"] == b["token_ids"]                   # deterministic kernels, same trees
+    engine.end_session()
+
+
+def test_eager_kernel_batches(engine, small):
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 4096, (1, n), generator=g) for n in (9, 33, 20)]
+    sp = SamplingParams(0.0, 12)
+    outs = engine.generate_batch(prompts, sp)
+    touts = engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=7), block_size=5, tree_width=2, budget=8,
+                                       sampling_params=sp)
+    for p, o, t in zip(prompts, outs, touts):
+        for res in (o, t):
+            assert len(res["token_ids"]) == 12
+            agree, short = teacher_forced_agreement(small, p, res["token_ids"])
+            assert agree > 0.85 and short < 0.05

@@ -202,7 +202,8 @@ def test_device_tree_build_and_accept_match_host(ext, seed):
     st = ext.status_word(dev)
     s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     tk, lp, cp = i32(toks), torch.tensor(lps, dtype=torch.float32, device=dev), i32(caps)
-    assert lib.js_tree_build(p(tk), p(lp), p(cp), D, K, budget, NB, W, p(committed), p(state), p(slot_row), max_len,
+    zero = i32([0])
+    assert lib.js_tree_build(p(tk), p(lp), p(cp), D, K, budget, NB, W, p(committed), p(state), p(slot_row), p(zero), max_len,
                              p(o["tok"]), p(o["par"]), p(o["dep"]), p(o["pos"]), p(o["slot"]), p(bits), p(st), 0, s) == 0
     torch.cuda.synchronize()
     n = host.num_nodes
@@ -223,8 +224,8 @@ def test_device_tree_build_and_accept_match_host(ext, seed):
     result = torch.zeros(64, dtype=torch.int32, device=dev)
     eos = i32([49])
     assert lib.js_tree_accept_commit(p(o["tok"]), p(o["par"]), p(o["dep"]), p(greedy), NB, p(state), p(slot_row),
-                                     max_len, p(committed), max_len, p(eos), 1, 1000, p(path_idx), p(result), p(st),
-                                     0, s) == 0
+                                     p(zero), max_len, p(committed), max_len, p(eos), 1, 1000, p(path_idx), p(result),
+                                     p(st), 0, s) == 0
     torch.cuda.synchronize()
     assert int(result[0]) == acc_h and int(result[1]) == int(corr_h)
     assert path_idx[:acc_h + 1].tolist() == path_h.tolist()
