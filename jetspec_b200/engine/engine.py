@@ -90,7 +90,7 @@ class JetSpecEngine:
                  block_size: int = 16, attn_implementation: str = "sdpa", attn_backend: str = "sm100",
                  fuse_gemms: bool = False, torch_compile: bool = False, fused_moe: bool = False, *,
                  tokenizer=None, num_pages: Optional[int] = None, max_seqs: int = 64,
-                 max_seq_len: int = 8192, use_kernels: Optional[bool] = None):
+                 max_seq_len: int = 8192, use_kernels: Optional[bool] = None, tensor_parallel=None):
         if attn_backend not in _BACKEND_ALIASES:
             raise ValueError(f"unknown attn_backend {attn_backend!r}; expected one of {sorted(_BACKEND_ALIASES)}")
         if isinstance(model_name_or_path, Qwen3ForCausalLM):
@@ -119,19 +119,21 @@ class JetSpecEngine:
         self.use_kernels = (dev.type == "cuda" and dtype == torch.bfloat16) if use_kernels is None else bool(use_kernels)
         self._fast = None
         self.last_stats: dict = {}
+        self.tp = tensor_parallel      # jetspec_b200.parallel.TensorParallel or None
 
     # ------------------------------------------------------------------ pool
     def _ensure_pool(self, tokens_needed: int, seqs: int = 1) -> PagedKVPool:
         """Create (or grow, when nothing is resident) the KV pool."""
-        want_pages = (tokens_needed + self.block_size - 1) // self.block_size + seqs
+        need_pages = (tokens_needed + self.block_size - 1) // self.block_size + seqs
+        want_pages = need_pages
         if self._num_pages is not None:
-            want_pages = int(self._num_pages)      # an explicit size is a hard size
+            want_pages = need_pages = int(self._num_pages)      # an explicit size is a hard size
         elif self.use_kernels:
             # captured graphs pin the pool: size it once for a full-length sequence
             want_pages = max(want_pages, (self._max_seq_len + self.block_size - 1) // self.block_size + seqs)
         max_len = max(self._max_seq_len, int(math.ceil(tokens_needed / max(1, seqs))) + self.block_size)
         if self.pool is not None:
-            fits = self.pool.num_pages >= want_pages and self.pool.max_seq_len >= max_len \
+            fits = self.pool.num_pages >= need_pages and self.pool.max_seq_len >= max_len \
                 and self.pool.max_seqs >= seqs
             if fits:
                 return self.pool

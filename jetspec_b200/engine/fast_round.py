@@ -97,9 +97,11 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
         X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
         X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
         n += 8 + (1 if st.splits > 1 else 0)
-        if taps is not None and li in tap_ids and li != last:
-            X.gather_rows(st.x, None, taps, dst_col0=tap_ids.index(li) * H, pdl=pdl)
-            n += 1
+        if taps is not None and li != last:
+            for j, t in enumerate(tap_ids):
+                if t == li:
+                    X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
+                    n += 1
     return n
 
 
@@ -124,6 +126,9 @@ class FastRound:
         self.graphs: dict = {}
         self.draft_cache: dict = {}
         self.launches_per_round = 0
+        self.timing = False            # when set, each graph replay is bracketed by CUDA events
+        self.last_device_ms = 0.0      # summed device time of the last call's rounds
+        self.last_rounds = 0
 
     # ------------------------------------------------------------------ support matrix
     def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget) -> bool:
@@ -296,9 +301,11 @@ class FastRound:
                                 self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl)
         X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
         last = cfg.num_hidden_layers - 1
-        if r["taps"] is not None and last in r["tap_ids"]:
-            X.gather_rows(r["xn"], None, r["taps"], dst_col0=r["tap_ids"].index(last) * cfg.hidden_size, pdl=pdl)
-            n += 1
+        if r["taps"] is not None:
+            for j, t in enumerate(r["tap_ids"]):
+                if t == last:
+                    X.gather_rows(r["xn"], None, r["taps"], dst_col0=j * cfg.hidden_size, pdl=pdl)
+                    n += 1
         X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
         X._check(lib.js_tree_accept_commit(p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["greedy"]), NB,
                                            p(r["state"]), p(pool.slot_map), p(r["seq_rows"]), pool.max_seq_len,
@@ -372,6 +379,7 @@ class FastRound:
         stage_tok, stage_lp, stage_caps = r["stage_tok"].numpy(), r["stage_lp"].numpy(), r["stage_caps"].numpy()
         src = oracle if oracle is not None else host_drafter
         stream = torch.cuda.current_stream()
+        events = []
         while len(new_ids) < sp.max_new_tokens and not done:
             if staged:
                 ctx_t = torch.tensor([ctx_ids], dtype=torch.long, device="cpu" if oracle is not None else eng.device)
@@ -384,7 +392,14 @@ class FastRound:
                 stage_lp[:] = np.asarray(lp_l, dtype=np.float32)
                 stage_caps[:] = np.asarray(algo_obj.caps_from_topk(lp_l, K, prompt_info=prompt_info,
                                                                    profile_table=profile_table), dtype=np.int32)
-            r["graph"].replay()
+            if self.timing:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                r["graph"].replay()
+                e1.record(stream)
+                events.append((e0, e1))
+            else:
+                r["graph"].replay()
             stream.synchronize()
             rounds += 1
             acc, n_nodes = int(res[0]), int(res[3])
@@ -404,6 +419,8 @@ class FastRound:
                     break
         if rounds:
             eng.pool.state(sid).length = int(res[4])
+        self.last_rounds = rounds
+        self.last_device_ms = float(sum(a.elapsed_time(b) for a, b in events)) if events else 0.0
         new_ids = new_ids[: sp.max_new_tokens]
         out = {"token_ids": new_ids, "text": decode_text(eng.tokenizer, new_ids),
                "tpf": (len(new_ids) / rounds if rounds else 0.0)}

@@ -177,8 +177,8 @@ class Qwen3ForCausalLM(nn.Module):
         """
         cfg = self.config
         x = self.model.embed_tokens(input_ids)
-        taps = [] if tap_layers is not None else None
-        tap_set = list(tap_layers) if tap_layers is not None else []
+        tap_ids = list(tap_layers) if tap_layers is not None else None
+        tapped = {}
         last = cfg.num_hidden_layers - 1
         for li, layer in enumerate(self.model.layers):
             a = layer.self_attn
@@ -197,15 +197,12 @@ class Qwen3ForCausalLM(nn.Module):
                 x = x + layer.mlp(h, rl)
             else:
                 x = x + layer.mlp(h)
-            if taps is not None and li in tap_set and li != last:
-                taps.append((tap_set.index(li), x))
+            if tap_ids is not None and li in tap_ids and li != last:
+                tapped[li] = x
         xn = self.model.norm(x)
-        if taps is not None and last in tap_set:
-            taps.append((tap_set.index(last), xn))
-        tap_cat = None
-        if taps is not None:
-            taps.sort(key=lambda t: t[0])
-            tap_cat = torch.cat([t[1] for t in taps], dim=-1) if taps else None
+        if tap_ids is not None and last in tap_ids:
+            tapped[last] = xn
+        tap_cat = torch.cat([tapped[i] for i in tap_ids], dim=-1) if tap_ids else None
         rows = xn if logits_rows is None else xn[logits_rows]
         logits = ops.linear(rows, self.lm_head.weight)
         if return_hidden:
@@ -230,9 +227,18 @@ class Qwen3ForCausalLM(nn.Module):
 
 
 def _fill_normal_(p: torch.Tensor, std: float, g: torch.Generator, chunk: int = 1 << 24) -> None:
-    """Seeded normal fill that is identical on every device (drawn on the host in chunks)."""
+    """Seeded normal fill.  Small tensors are drawn on the host (identical on every device);
+    tensors above 4M elements that live on a GPU are drawn there with a generator seeded from
+    the host stream, which keeps multi-billion-parameter synthetic models quick to build."""
     flat = p.view(-1)
     n = flat.numel()
+    if p.is_cuda and n > (1 << 22):
+        seed = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=g))
+        dg = torch.Generator(device=p.device).manual_seed(seed)
+        for s in range(0, n, chunk):
+            e = min(n, s + chunk)
+            flat[s:e] = (torch.randn(e - s, generator=dg, dtype=torch.float32, device=p.device) * std).to(p.dtype)
+        return
     for s in range(0, n, chunk):
         e = min(n, s + chunk)
         flat[s:e] = (torch.randn(e - s, generator=g, dtype=torch.float32) * std).to(p.dtype).to(p.device)
