@@ -1,10 +1,196 @@
-"""Runs the unmodified reference package on the benchmark configuration.
+"""Runs the UNMODIFIED reference package (installed under ``baseline/_ref``) on the benchmark
+configuration and prints the same JSON line as ``bench.py`` with ``"impl": "reference"``.
 
-Filled in by :func:`run_reference`; prints the same JSON line as ``bench.py`` with
-``"impl": "reference"``, or ``{"impl": "reference", "unavailable": "<why>"}``.
+The reference loads models with Hugging Face ``from_pretrained``, so the synthetic target and
+draft head are first written to a scratch directory in the stock checkpoint format (the same
+seeded weights our own arm uses) together with a minimal word-level tokenizer; prompts are
+passed as token ids.  The engine is then built and driven exactly as the reference's own
+throughput script does (``bench/engine/tps_walltime.py:205-275``): backend
+``triton_paged_tree_cudagraph_nogather``, fused GEMMs, ``GraphedDraftHead``, ``session=True``.
+The reference has no tensor parallelism: for N > 1 only rank 0 runs it, on one GPU.
+
+If any step the reference needs cannot run on this box, the function prints
+``{"impl": "reference", "unavailable": "<why>"}`` and returns.
 """
+from __future__ import annotations
+
 import json
+import os
+import shutil
+import sys
+import tempfile
+import time
+import traceback
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+
+
+def _unavailable(why: str):
+    print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}), flush=True)
+
+
+def write_tokenizer(path: str, vocab_size: int) -> None:
+    """A word-level tokenizer with ``vocab_size`` dummy entries, enough for ``AutoTokenizer``."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    vocab = {f"t{i}": i for i in range(vocab_size)}
+    tok = Tokenizer(models.WordLevel(vocab=vocab, unk_token="t0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="t0", pad_token="t0").save_pretrained(path)
+
+
+def write_hf_config(path: str, cfg, extra: dict | None = None) -> None:
+    """``config.json`` in the stock Qwen3 layout."""
+    d = {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": cfg.vocab_size,
+        "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+        "num_hidden_layers": cfg.num_hidden_layers, "num_attention_heads": cfg.num_attention_heads,
+        "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "hidden_act": "silu",
+        "max_position_embeddings": cfg.max_position_embeddings, "rms_norm_eps": cfg.rms_norm_eps,
+        "rope_theta": cfg.rope_theta, "tie_word_embeddings": False, "attention_bias": False,
+        "attention_dropout": 0.0, "use_cache": True, "torch_dtype": "bfloat16", "sliding_window": None,
+        "use_sliding_window": False, "max_window_layers": cfg.num_hidden_layers,
+    }
+    d.update(extra or {})
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(d, f, indent=1)
+
+
+def build_checkpoints(args, scratch: str, device: str):
+    """Write target + draft head (our seeded synthetic weights) in Hugging Face format."""
+    import torch
+    from bench import model_config
+    from jetspec_b200.models import Qwen3ForCausalLM, DraftHeadModel, draft_head_config
+    from jetspec_b200.models.loader import save_state
+    cfg = model_config(args.model)
+    bs = args.tree_depth + 1
+    tdir, hdir = os.path.join(scratch, "target"), os.path.join(scratch, "head")
+    model = Qwen3ForCausalLM.random_init(cfg, seed=args.seed, dtype=torch.bfloat16, device=device, init="stable")
+    write_hf_config(tdir, cfg)
+    save_state(dict(model.state_dict()), tdir)
+    write_tokenizer(tdir, cfg.vocab_size)
+    del model
+    hcfg = draft_head_config(cfg, num_layers=1, block_size=bs, num_taps=5)
+    head = DraftHeadModel.random_init(hcfg, seed=args.seed + 1, dtype=torch.bfloat16, device=device)
+    write_hf_config(hdir, hcfg, {"architectures": ["DFlashDraftModel"], "block_size": bs,
+                                 "num_target_layers": cfg.num_hidden_layers, "dflash_config": hcfg.dflash_config,
+                                 "layer_types": ["full_attention"] * hcfg.num_hidden_layers})
+    save_state(dict(head.state_dict()), hdir)
+    del head
+    torch.cuda.empty_cache()
+    return cfg, tdir, hdir
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}))
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl")
+    try:
+        if rank == 0:
+            _run(args, world)
+    except Exception as e:  # noqa: BLE001 - any failure of the reference stack is reported, not raised
+        tb = traceback.format_exc().strip().splitlines()
+        _unavailable(f"{type(e).__name__}: {e} | {tb[-3] if len(tb) >= 3 else ''}")
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+def _run(args, world: int):
+    if not os.path.isdir(os.path.join(REF, "jetspec")):
+        return _unavailable("reference package is not installed under baseline/_ref")
+    import torch
+    if not torch.cuda.is_available():
+        return _unavailable("no CUDA device")
+    sys.path.insert(0, REF)
+    root = os.path.dirname(HERE)
+    if root not in sys.path:
+        sys.path.insert(1, root)
+    os.environ.setdefault("JETSPEC_FUSE_GEMMS", "1")
+    cache = os.path.join(tempfile.gettempdir(), "jetspec_ref_cache")
+    os.environ.setdefault("TORCHINDUCTOR_CACHE_DIR", os.path.join(cache, "inductor"))
+    os.environ.setdefault("TRITON_CACHE_DIR", os.path.join(cache, "triton"))
+    from bench import ClockSampler, BASELINE_TOK_S
+    from jetspec_b200.drafters import OracleTreeDrafter, OracleOverrideDrafter
+    dev = "cuda:0" if world == 1 else f"cuda:{os.environ.get('LOCAL_RANK', '0')}"
+    scratch = tempfile.mkdtemp(prefix="jetspec_ref_")
+    try:
+        cfg, tdir, hdir = build_checkpoints(args, scratch, dev)
+        from jetspec.inference_engine import JetSpecEngine, SamplingParams
+        from jetspec import load_draft_head
+        from jetspec.draft_head_adapter import GraphedDraftHead
+        eng = JetSpecEngine(tdir, device=dev, dtype=torch.bfloat16, block_size=16, attn_implementation="sdpa",
+                            attn_backend="triton_paged_tree_cudagraph_nogather", fuse_gemms=True)
+        head = load_draft_head(hdir, device=dev, dtype=torch.bfloat16, attn_implementation=eng.resolved_attn_implementation)
+        bs = args.tree_depth + 1
+        real = GraphedDraftHead(head, target=eng.model, block_size=bs, target_layer_ids=head.target_layer_ids,
+                                draft_shift=False)
+        prompt = torch.randint(0, cfg.vocab_size, (1, args.prompt_len),
+                               generator=torch.Generator().manual_seed(args.seed)).pin_memory()
+        sp = SamplingParams(0.0, args.max_new)
+        cont = prompt[0].tolist() + eng.generate(prompt, sp)["token_ids"]
+        max_accept = min(args.tree_depth, (args.budget - 2) // args.tree_width + 1)
+        oracle = OracleTreeDrafter(cont, cfg.vocab_size, tree_width=args.tree_width, mean_accept=args.mean_accept,
+                                   max_accept=max_accept, seed=args.seed)
+        drafter = OracleOverrideDrafter(real, oracle)
+        kw = dict(block_size=bs, tree_width=args.tree_width, budget=args.budget, tree_depth=args.tree_depth,
+                  algo="accum_logp", target_layer_ids=head.target_layer_ids, return_stats=True, sampling_params=sp,
+                  session=True, session_prompt_capacity=((args.prompt_len + 255) // 256) * 256)
+        converged = False
+        for it in range(6):
+            out = eng.generate_tree(prompt, drafter, **kw)
+            seq = prompt[0].tolist() + out["token_ids"]
+            if seq == oracle.sequence[:len(seq)]:
+                converged = True
+                break
+            oracle.set_continuation(seq)
+        for _ in range(args.warmup):
+            eng.generate_tree(prompt, drafter, **kw)
+        sampler = ClockSampler(torch.cuda.current_device())
+        torch.cuda.synchronize()
+        sampler.start()
+        toks, rounds, accept = 0, 0, []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(args.steps):
+            out = eng.generate_tree(prompt, drafter, **kw)
+            toks += len(out["token_ids"])
+            rounds += out["rounds"]
+            accept += out["accept_lengths"]
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        dev_ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        value = toks / (dev_ms / 1e3)
+        D, K = args.tree_depth, args.tree_width
+        print(json.dumps({
+            "metric": "decode tokens/s/request, Qwen3-8B tree budget 128", "value": round(value, 2),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_TOK_S, 4), "dtype": "bf16", "data": "synthetic",
+            "impl": "reference",
+            "config": {"model": f"{args.model} (random init, residual-dominant variant)", "global_batch": 1,
+                       "seq_len": args.prompt_len + args.max_new, "parallelism": "tp1 (the reference has no TP)",
+                       "backend": "triton_paged_tree_cudagraph_nogather + fuse_gemms + GraphedDraftHead + session",
+                       "tree": f"depth {D} width {K} budget {args.budget}",
+                       "mean_tokens_per_round": round(sum(accept) / max(1, len(accept)), 3),
+                       "ms_per_round": round(dev_ms / max(1, rounds), 4), "oracle_converged": converged,
+                       "timing": "CUDA events around whole requests (prefill included)",
+                       "l2": "inputs larger than L2 (16 GB of weights per round)"},
+            "clocks": clocks,
+            "e2e": {"value": round(toks / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": args.prompt_len * 8,
+                    "d2h_bytes_per_step": int(rounds / args.steps * 16)},
+            "gpu_launches": 0,
+        }), flush=True)
+    finally:
+        shutil.rmtree(scratch, ignore_errors=True)

@@ -206,12 +206,17 @@ __global__ void __launch_bounds__(ATHREADS, 2) paged_tree_attn_kernel(AttnParams
         mx[e >> 1] = fmaxf(mx[e >> 1], x);
       }
     }
+    // The running maximum is kept as an INTEGER (in the log2 domain).  Probabilities are then
+    // 2^(s - m) with m integral, so choosing a different m (another tile order, another key
+    // split) only moves them by an exact power of two: the bf16 rounding of P and every
+    // rescale are bit-identical whatever the KV layout.  A node's attention output therefore
+    // does not depend, beyond fp32 summation order, on where its ancestors sit in the window.
     float alpha[2], m_new[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      m_new[i] = fmaxf(m_run[i], mx[i]);
+      m_new[i] = fmaxf(m_run[i], ceilf(mx[i]));
       const float m_safe = (m_new[i] == -INFINITY) ? 0.f : m_new[i];   // all-masked row guard
       alpha[i] = exp2f(m_run[i] - m_safe);
       m_run[i] = m_new[i];

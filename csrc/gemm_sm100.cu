@@ -71,7 +71,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kData);
+  // the split-K partial tile reuses the pipeline stages; it only needs extra room when it is larger
+  const int data_bytes = (gridDim.z > 1 && S::kRed > S::kTiles) ? S::kRed : S::kTiles;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + data_bytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* accum_bar = empty_bar + kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
@@ -274,8 +276,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int gc = n0 + c0 + j;
-          // the values feed an argmax over bf16-rounded logits, like the unfused reference
-          const float x = __bfloat162float(__float2bfloat16_rn(v[j]));
+          // compare the fp32 accumulators: rounding the logits to bf16 first would turn the many
+          // near-ties of a 150k-entry vocabulary into exact ties decided by index order
+          const float x = v[j];
           if (gc < p.N && x > best) { best = x; best_i = gc; }
         }
       }
@@ -373,7 +376,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.dynamicSmemBytes = ((split > 1 && S::kRed > S::kTiles) ? S::kRed : S::kTiles) + 1024 + 256;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int na = 0;

@@ -113,18 +113,38 @@ class Qwen3ForCausalLM(nn.Module):
     # -- construction ---------------------------------------------------------
     @classmethod
     def random_init(cls, cfg: Qwen3Config, seed: int = 0, dtype=torch.float32, device="cpu",
-                    std: float = 0.02) -> "Qwen3ForCausalLM":
-        """N(0, std) weights, unit norm scales: the synthetic-weights convention of the benchmarks."""
+                    std: float = 0.02, init: str = "normal") -> "Qwen3ForCausalLM":
+        """Synthetic weights.
+
+        ``init="normal"``: every matrix N(0, std), norm scales 1.
+
+        ``init="stable"``: a residual-dominant variant for benchmarks whose drafter is scripted
+        from the target's own greedy continuation.  A deep N(0, 0.02) network has near-tied
+        logits (top-1/top-2 gap of a few percent) that flip with the last bf16 bit, so its
+        greedy continuation differs between any two kernels or KV layouts and no script
+        survives.  Here the embedding is N(0, 1), the output projections (``o_proj``,
+        ``down_proj``) are N(0, std / sqrt(2 L)) as in scaled-init schemes, and the LM head is
+        the embedding table shifted by one row, so the greedy next token of ``t`` is ``t + 1``
+        with a wide margin.  Shapes, dtypes and therefore all kernel work are unchanged.
+        """
         with torch.device("meta"):
             m = cls(cfg)
         m = m.to_empty(device=device).to(dtype)
         g = torch.Generator(device="cpu").manual_seed(seed)
+        out_scale = 1.0 / (2.0 * cfg.num_hidden_layers) ** 0.5
         with torch.no_grad():
             for name, p in m.named_parameters():
                 if name.endswith("norm.weight") or "layernorm" in name:
                     p.fill_(1.0)
+                elif init == "stable" and name.endswith("embed_tokens.weight"):
+                    _fill_normal_(p, 1.0, g)
+                elif init == "stable" and (name.endswith("o_proj.weight") or name.endswith("down_proj.weight")
+                                           or name.endswith("w_down")):
+                    _fill_normal_(p, std * out_scale, g)
                 else:
                     _fill_normal_(p, std, g)
+            if init == "stable":
+                m.lm_head.weight.copy_(torch.roll(m.model.embed_tokens.weight, 1, dims=0))
         return m.eval()
 
     @classmethod

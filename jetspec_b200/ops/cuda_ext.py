@@ -149,6 +149,10 @@ SM_COUNT = 148
 _DEEP = os.environ.get("JETSPEC_GEMM_DEEP", "0") == "1"
 
 
+# measured best (bn, split, deep) per (M, N, K, epilogue); filled from the tuning sweep
+GEMM_TUNING: dict = {}
+
+
 def gemm_supported(M: int, N: int, K: int) -> bool:
     return K % 8 == 0 and N % 8 == 0 and K >= 64
 
@@ -160,6 +164,9 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int):
     SMs (two CTAs fit per SM with the shallow pipeline) without re-reading the
     activations more than necessary.
     """
+    key = (M, N, K, epi)
+    if key in GEMM_TUNING:
+        return GEMM_TUNING[key]
     bn = 128
     m_tiles = (M + 127) // 128
     tiles = m_tiles * ((N + bn - 1) // bn)
