@@ -156,6 +156,16 @@ JS_DEVICE float ld_dsmem_f32(uint32_t cluster_addr) {
   return v;
 }
 
+JS_DEVICE void st_dsmem_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+JS_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 JS_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 JS_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

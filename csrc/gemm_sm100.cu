@@ -43,7 +43,18 @@ struct GemmParams {
   int* part_idx;                // ARGMAX: [M, n_tiles] ; TOPK: [M, n_tiles, 8] indices
   float* part_lse;              // TOPK: [M, n_tiles, 2] (running max, sum of exp)
   int* status;
+  unsigned long long* trace;    // optional: 8 phase timestamps (ns) written by CTA (0,0,0)
 };
+
+JS_DEVICE unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define JS_TRACE(slot)                                                                     \
+  do {                                                                                     \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[slot] = gtime(); \
+  } while (0)
 
 // BUDGET_KB bounds the pipeline's shared memory: ~96 KB lets two CTAs share an SM (more tiles
 // in flight, natural load balance when the tile count is not a multiple of 148), ~192 KB gives
@@ -57,10 +68,18 @@ struct GemmSmem {
   static constexpr int kStages = (kBudget / kStage) > 8 ? 8 : ((kBudget / kStage) < 2 ? 2 : (kBudget / kStage));
   static constexpr int kMinBlocks = BUDGET_KB <= 100 ? 2 : 1;
   static constexpr int kTiles = kStages * kStage;
-  static constexpr int kRed = BN * BM * 4;   // split-K partial tile, column-major fp32
-  static constexpr int kData = kTiles > kRed ? kTiles : kRed;
-  static constexpr int kBytes = kData + 1024 /*align slack*/ + 256 /*barriers*/;
 };
+
+// Split-K receive area: every CTA of the cluster owns some 32-column chunks of the tile and gets,
+// from each source CTA, one 16 KB slot (32 columns x 128 rows fp32, column-major) per owned chunk.
+__host__ __device__ inline int recv_slots_per_src(int split, int bn, bool swiglu) {
+  const int hc = (swiglu ? bn / 2 : bn) / 32;
+  const int per = (hc + split - 1) / split;
+  return swiglu ? 2 * per : per;
+}
+__host__ __device__ inline int recv_bytes(int split, int bn, bool swiglu) {
+  return split > 1 ? split * recv_slots_per_src(split, bn, swiglu) * 16384 : 0;
+}
 
 template <int BN, int EPI, int BUDGET_KB>
 __global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB>::kMinBlocks)
@@ -71,8 +90,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // the split-K partial tile reuses the pipeline stages; it only needs extra room when it is larger
-  const int data_bytes = (gridDim.z > 1 && S::kRed > S::kTiles) ? S::kRed : S::kTiles;
+  // [pipeline stages][split-K receive area][barriers]; the receive area is separate from the
+  // stages because peers push into it while this CTA may still be streaming
+  const int data_bytes = S::kTiles + recv_bytes(gridDim.z, BN, EPI == EPI_SWIGLU);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + data_bytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* accum_bar = empty_bar + kStages;
@@ -90,6 +110,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int nkb = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
+    JS_TRACE(0);   // kernel start
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmW);
     for (int s = 0; s < kStages; ++s) {
@@ -114,6 +135,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
+      JS_TRACE(1);   // setup done, first TMA about to issue
       // Weights do not depend on the previous kernel: start streaming them before waiting on it.
       const int pre = nkb < kStages ? nkb : kStages;
       for (int i = 0; i < pre; ++i) {
@@ -141,6 +163,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t ph = (i / kStages) & 1;
         ok = mbar_wait(&full_bar[s], ph, p.status, kTimeoutFull);
         if (!ok) break;
+        if (i == 0) JS_TRACE(2);   // first stage landed
         tc_fence_after();
         const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage));
         const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage + S::kStageA));
@@ -161,34 +184,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int row = quad * 32 + lane;              // row of the tile owned by this thread
   const int grow = m0 + row;
   const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-  float* red = reinterpret_cast<float*>(smem);   // [BN][128] column-major partial (split-K only)
+  // split-K: this CTA's receive area (after the pipeline stages) and the chunk -> owner mapping
+  constexpr bool kSwiglu = (EPI == EPI_SWIGLU);
+  constexpr int kHC = (kSwiglu ? BN / 2 : BN) / 32;          // owned-chunk index space
+  const int per_owner = (kHC + split - 1) / split;
+  const int slots_per_src = kSwiglu ? 2 * per_owner : per_owner;
+  const uint32_t recv_addr = smem_u32(smem + S::kTiles);
+  // TMEM chunk `ch` (32 columns) is finished by CTA owner_of(ch); local_of(ch) is its slot there
+  auto owner_of = [&](int ch) { return (ch % kHC) % split; };
+  auto local_of = [&](int ch) { return (ch % kHC) / split + (ch >= kHC ? per_owner : 0); };
   bool acc_ok = true;
 
   if (epi_warp) {
     pdl_wait();   // residual / C may be produced by the previous kernel
     acc_ok = mbar_wait(accum_bar, 0, p.status, kTimeoutAccum);
     tc_fence_after();
+    if (threadIdx.x == 64) JS_TRACE(3);   // accumulator complete
   }
 
   if (split > 1) {
-    // park the partial tile in shared memory (the pipeline stages are idle now)
+    // push every chunk of the partial tile into its owner's receive area (remote stores are
+    // fire-and-forget; the cluster barrier below makes them visible)
     if (epi_warp && acc_ok) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int ch = 0; ch < BN / 32; ++ch) {
         uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_32x32(t_row + ch * 32, r);
         tmem_ld_wait();
+        const uint32_t dst = map_to_cta(recv_addr, owner_of(ch)) +
+                             static_cast<uint32_t>((z * slots_per_src + local_of(ch)) * 16384 + row * 4);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) red[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) st_dsmem_f32(dst + j * (BM * 4), __uint_as_float(r[j]));
       }
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 64) JS_TRACE(4);   // partial tile pushed
     cluster_sync();
+    if (threadIdx.x == 64) JS_TRACE(5);   // every peer's partial has landed here
   }
 
   if (epi_warp && acc_ok) {
-    const uint32_t red_addr = smem_u32(red);
+    const float* recv = reinterpret_cast<const float*>(smem + S::kTiles);
     // fetch 32 consecutive accumulator columns of this thread's row, reduced over the K split
     auto load_chunk = [&](int c0, float* v) {
       if (split == 1) {
@@ -200,10 +237,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        for (int pr = 0; pr < split; ++pr) {
-          const uint32_t base = map_to_cta(red_addr, pr) + (c0 * BM + row) * 4;
+        const int lo = local_of(c0 >> 5);
+        for (int src = 0; src < split; ++src) {   // fixed source order: deterministic sum
+          const float* base = recv + (src * slots_per_src + lo) * 4096 + row;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] += ld_dsmem_f32(base + j * BM * 4);
+          for (int j = 0; j < 32; ++j) v[j] += base[j * BM];
         }
       }
     };
@@ -323,13 +361,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == 64) JS_TRACE(6);     // epilogue stores issued
   tc_fence_before();
   __syncthreads();
-  if (split > 1) cluster_sync();   // peers may still be reading this CTA's partial tile
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) JS_TRACE(7);      // kernel end
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -367,16 +406,18 @@ template <int BN, int EPI, int BUDGET_KB>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
                        cudaStream_t stream) {
   using S = GemmSmem<BN, BUDGET_KB>;
-  static bool configured = false;
+  static int configured = 0;
   auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess) return -3;
-    configured = true;
+  const int smem_bytes = S::kTiles + recv_bytes(split, BN, EPI == EPI_SWIGLU) + 1024 /*align slack*/ + 256 /*barriers*/;
+  if (smem_bytes > 227 * 1024) return -18;
+  if (smem_bytes > configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;
+    configured = smem_bytes;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = ((split > 1 && S::kRed > S::kTiles) ? S::kRed : S::kTiles) + 1024 + 256;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int na = 0;
@@ -402,7 +443,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
 // one-CTA-per-SM deep pipeline instead of the two-CTAs-per-SM one.  Returns 0 or a negative code.
 extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* residual, int M, int N, int K, int lda,
                             int ldw, int ldc, int epi, int bn, int split, int deep, float* part_val, int* part_idx,
-                            float* part_lse, int* status, int pdl, cudaStream_t stream) {
+                            float* part_lse, int* status, unsigned long long* trace, int pdl,
+                            cudaStream_t stream) {
   using namespace js;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8)) return -10;           // TMA: 16-byte aligned rows
@@ -415,11 +457,12 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   if ((epi == EPI_STORE || epi == EPI_SWIGLU) && (ldc % 8)) return -15;
   CUtensorMap ta, tw;
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, bn)) return -16;
-  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status};
+  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace};
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
-    return deep ? launch_gemm<BN_, EPI_, 192>(ta, tw, p, split, pdl != 0, stream)                       \
-                : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
+    return (split > 1 && BN_ < 256) ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
+           : (deep && split == 1)   ? launch_gemm<BN_, EPI_, 192>(ta, tw, p, split, pdl != 0, stream)   \
+                                    : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
   JS_CASE(64, EPI_STORE) JS_CASE(128, EPI_STORE) JS_CASE(256, EPI_STORE)
   JS_CASE(128, EPI_STORE_F32)
   JS_CASE(128, EPI_SWIGLU) JS_CASE(256, EPI_SWIGLU)

@@ -172,18 +172,25 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int):
     tiles = m_tiles * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
     split = 1
+    deep = _DEEP
     if epi in (EPI_STORE, EPI_STORE_F32, EPI_SWIGLU):
         max_split = 4 if epi != EPI_SWIGLU else 2
+        # first choice: one CTA per SM with the deep pipeline (fewest CTAs that still cover the chip)
+        one = 1
+        while one < max_split and tiles * (one + 1) <= SM_COUNT and kb // (one + 1) >= 4:
+            one += 1
+        if tiles * one >= SM_COUNT * 3 // 4 and tiles * one <= SM_COUNT:
+            return bn, one, True
         slots = 2 * SM_COUNT
         while split < max_split and tiles * (split + 1) <= slots and kb // (split + 1) >= 4:
             split += 1
-    return bn, split, _DEEP
+    return bn, split, deep
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, epi: int = EPI_STORE, bn: Optional[int] = None,
          split: Optional[int] = None, deep: Optional[bool] = None, pdl: bool = False,
-         part_val=None, part_idx=None, part_lse=None) -> torch.Tensor:
+         part_val=None, part_idx=None, part_lse=None, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = x @ w.T`` (+ ``residual``) on the tcgen05 kernel.  ``x (M, K)``, ``w (N, K)`` bf16."""
     lib = load()
     M, K = x.shape
@@ -203,7 +210,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     ldc = out.stride(0) if out is not None else 0
     rc = lib.js_gemm_bf16(_p(x), _p(w), _p(out), _p(residual), M, N, K, x.stride(0), w.stride(0), ldc, epi, bn,
                           split, int(bool(deep)), _p(part_val), _p(part_idx), _p(part_lse),
-                          _p(status_word(x.device)), int(pdl), _stream())
+                          _p(status_word(x.device)), _p(trace), int(pdl), _stream())
     _check(rc, f"js_gemm_bf16(M={M},N={N},K={K},epi={epi},bn={bn},split={split})")
     return out
 
