@@ -32,7 +32,7 @@ constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kTopK = 8;
 
-enum GemmEpi : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_TOPK = 3, EPI_STORE_F32 = 4 };
+enum GemmEpi : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_TOPK = 3, EPI_STORE_F32 = 4, EPI_ALLREDUCE = 5 };
 
 struct GemmParams {
   int M, N, K;
@@ -44,7 +44,21 @@ struct GemmParams {
   float* part_lse;              // TOPK: [M, n_tiles, 2] (running max, sum of exp)
   int* status;
   unsigned long long* trace;    // optional: 8 phase timestamps (ns) written by CTA (0,0,0)
+  // EPI_ALLREDUCE (tensor-parallel row-parallel GEMM): every rank's receive buffer and flag array
+  __nv_bfloat16* const* peer_recv;  // [world] -> (world, m_cap, N) bf16 on that rank
+  int* const* peer_flags;           // [world] -> one counter per CTA of this grid on that rank
+  int rank, world, m_cap;
 };
+
+JS_DEVICE void red_release_sys_add(int* addr, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+JS_DEVICE int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+JS_DEVICE void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the 4 epilogue warps
 
 JS_DEVICE unsigned long long gtime() {
   unsigned long long t;
@@ -246,7 +260,97 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     };
 
-    if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
+    if constexpr (EPI == EPI_ALLREDUCE) {
+      // Row-parallel GEMM fused with the tensor-parallel all-reduce (one shot): each finished
+      // 32-column chunk of this rank's partial product is stored as bf16 straight into every
+      // rank's receive buffer over NVLink, a per-CTA counter on each rank is bumped with release
+      // semantics, and the CTA then waits (bounded) until all ranks' chunks have landed in ITS
+      // buffer, sums them in rank order together with the residual and writes the output.  All
+      // ranks add the same numbers in the same order, so the replicated result is bit-identical.
+      const int fidx = (blockIdx.y * gridDim.x + blockIdx.x) * split + z;
+      for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
+        float v[32];
+        load_chunk(c0, v);
+        const int gc = n0 + c0;
+        if (grow < p.M && gc < p.N) {
+          uint4 pk[4];
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(pk);
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o2[t] = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+          const size_t off = (static_cast<size_t>(p.rank) * p.m_cap + grow) * p.N + gc;
+          for (int r = 0; r < p.world; ++r) {
+            uint4* dst = reinterpret_cast<uint4*>(p.peer_recv[r] + off);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (gc + 8 * t < p.N) dst[t] = pk[t];
+          }
+        }
+      }
+      __threadfence_system();
+      epi_barrier();
+      bool landed = true;
+      if (threadIdx.x == 64) {
+        for (int r = 0; r < p.world; ++r) red_release_sys_add(p.peer_flags[r] + fidx, 1);
+        const int* mine = p.peer_flags[p.rank] + fidx;
+        landed = false;
+        for (uint32_t it = 0; it < (1u << 22); ++it) {
+          if (ld_acquire_sys(mine) >= p.world) { landed = true; break; }
+          __nanosleep(64);
+        }
+        if (!landed) report(p.status, kTimeoutPeer);
+        *reinterpret_cast<volatile int*>(tmem_slot + 1) = landed ? 1 : 0;
+      }
+      epi_barrier();
+      landed = *reinterpret_cast<volatile int*>(tmem_slot + 1) != 0;
+      if (landed) {
+        const __nv_bfloat16* mine = p.peer_recv[p.rank];
+        for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
+          const int gc = n0 + c0;
+          if (grow >= p.M || gc >= p.N) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          for (int src = 0; src < p.world; ++src) {
+            const uint4* sp = reinterpret_cast<const uint4*>(mine + (static_cast<size_t>(src) * p.m_cap + grow) * p.N + gc);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              if (gc + 8 * t >= p.N) break;
+              const uint4 rv = __ldcg(sp + t);     // written by a peer GPU: bypass L1
+              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(r2[u]);
+                v[8 * t + 2 * u] += f.x;
+                v[8 * t + 2 * u + 1] += f.y;
+              }
+            }
+          }
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
+          const __nv_bfloat16* res = p.residual ? p.residual + static_cast<size_t>(grow) * p.ldc + gc : nullptr;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (gc + 8 * t >= p.N) break;
+            if (res) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(res + 8 * t);
+              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(r2[u]);
+                v[8 * t + 2 * u] += f.x;
+                v[8 * t + 2 * u + 1] += f.y;
+              }
+            }
+            uint4 ov;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) o2[u] = __floats2bfloat162_rn(v[8 * t + 2 * u], v[8 * t + 2 * u + 1]);
+            *reinterpret_cast<uint4*>(out + 8 * t) = ov;
+          }
+        }
+      }
+      epi_barrier();
+      if (threadIdx.x == 64 && landed) p.peer_flags[p.rank][fidx] = 0;   // ready for this buffer's next turn
+    } else if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
       // 32-column chunks are dealt round-robin to the CTAs of the K-split cluster
       for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
         float v[32];
@@ -457,7 +561,8 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   if ((epi == EPI_STORE || epi == EPI_SWIGLU) && (ldc % 8)) return -15;
   CUtensorMap ta, tw;
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, bn)) return -16;
-  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace};
+  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace,
+               nullptr, nullptr, 0, 1, 0};
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
     return (split > 1 && BN_ < 256) ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
@@ -470,4 +575,30 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   JS_CASE(128, EPI_TOPK)
 #undef JS_CASE
   return -17;
+}
+
+// Tensor-parallel row-parallel GEMM fused with the all-reduce: out = residual + sum over ranks of
+// (A_rank[M,K_local] * W_rank[N,K_local]^T).  peer_recv / peer_flags are DEVICE arrays of `world`
+// pointers (every rank's receive buffer (world, m_cap, N) bf16 and per-CTA flag counters, this
+// rank's own included).  Every rank must call this with the same shapes, bn and split.
+extern "C" int js_gemm_bf16_allreduce(const void* A, const void* W, void* C, const void* residual, int M, int N, int K,
+                                      int lda, int ldw, int ldc, int split, void* const* peer_recv,
+                                      int* const* peer_flags, int rank, int world, int m_cap, int n_flags,
+                                      int* status, int pdl, cudaStream_t stream) {
+  using namespace js;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
+  const int kb_total = (K + BK - 1) / BK;
+  if (split < 1 || split > 4 || split > kb_total) return -12;
+  if (M > m_cap || world < 1 || rank < 0 || rank >= world) return -19;
+  const int ctas = ((N + 127) / 128) * ((M + BM - 1) / BM) * split;
+  if (ctas > n_flags) return -20;
+  if (ctas > (split > 1 ? 148 : 2 * 148)) return -21;   // every CTA must be resident: CTAs wait for peers on other GPUs
+  CUtensorMap ta, tw;
+  if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, 128)) return -16;
+  GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), nullptr, nullptr, nullptr, status,
+               nullptr, reinterpret_cast<__nv_bfloat16* const*>(peer_recv), peer_flags, rank, world, m_cap};
+  return split > 1 ? launch_gemm<128, EPI_ALLREDUCE, 128>(ta, tw, p, split, pdl != 0, stream)
+                   : launch_gemm<128, EPI_ALLREDUCE, 96>(ta, tw, p, split, pdl != 0, stream);
 }

@@ -110,6 +110,7 @@ class JetSpecEngine:
         from ..core.model_runner import ModelRunner
         self.runner = ModelRunner(self.model)
         self.cfg = self.model.config
+        self.tp = tensor_parallel      # jetspec_b200.parallel.TensorParallel or None
         self._num_pages = num_pages
         self._max_seqs, self._max_seq_len = int(max_seqs), int(max_seq_len)
         self.pool: Optional[PagedKVPool] = None
@@ -119,7 +120,6 @@ class JetSpecEngine:
         self.use_kernels = (dev.type == "cuda" and dtype == torch.bfloat16) if use_kernels is None else bool(use_kernels)
         self._fast = None
         self.last_stats: dict = {}
-        self.tp = tensor_parallel      # jetspec_b200.parallel.TensorParallel or None
 
     # ------------------------------------------------------------------ pool
     def _ensure_pool(self, tokens_needed: int, seqs: int = 1) -> PagedKVPool:
@@ -142,9 +142,11 @@ class JetSpecEngine:
                                    "construct the engine with a larger num_pages / max_seq_len")
             if self.pool.resident():
                 raise RuntimeError("cannot resize the KV pool while sequences are resident")
-        self.pool = PagedKVPool.for_model(self.cfg, max(want_pages, 2), page_size=self.block_size,
-                                          max_seqs=max(self._max_seqs, seqs), max_seq_len=max_len,
-                                          device=self.device, dtype=self.dtype)
+        world = self.tp.world if getattr(self, "tp", None) is not None else 1
+        self.pool = PagedKVPool(self.cfg.num_hidden_layers, self.cfg.num_key_value_heads // world, self.cfg.head_dim,
+                                max(want_pages, 2), page_size=self.block_size,
+                                max_seqs=max(self._max_seqs, seqs), max_seq_len=max_len,
+                                device=self.device, dtype=self.dtype)
         self._fast = None
         return self.pool
 

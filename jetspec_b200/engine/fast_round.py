@@ -37,9 +37,31 @@ def _i32(n, device, fill=0):
     return torch.full((n,), fill, dtype=torch.int32, device=device)
 
 
-def kernel_layer_weights(layers) -> list:
-    """Kernel-ready per-layer weights: fused QKV (and K|V alone), tile-interleaved gate/up."""
+def local_dims(cfg, world: int = 1):
+    """The per-rank view of a model's geometry under tensor parallelism."""
+    import types
+    return types.SimpleNamespace(
+        num_attention_heads=cfg.num_attention_heads // world, num_key_value_heads=cfg.num_key_value_heads // world,
+        head_dim=cfg.head_dim, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size // world,
+        rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta, vocab_size=cfg.vocab_size,
+        num_hidden_layers=cfg.num_hidden_layers)
+
+
+def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
+    """Kernel-ready per-layer weights: fused QKV (and K|V alone), tile-interleaved gate/up; with
+    tensor parallelism, this rank's shards of them."""
     out = []
+    if tp is not None:
+        from ..parallel.tp import shard_attention, shard_mlp
+        for layer in layers:
+            if not isinstance(layer.mlp, MLP) or layer.self_attn.q_proj.bias is not None:
+                raise NotImplementedError("the tensor-parallel graph path covers dense, bias-free layers")
+            d = {"ln1": layer.input_layernorm.weight, "ln2": layer.post_attention_layernorm.weight}
+            d.update(shard_attention(layer, cfg, tp.rank, tp.world))
+            m = shard_mlp(layer.mlp, tp.rank, tp.world, lambda g, u: X.interleave_gate_up(g, u, 128))
+            d.update({"gu": m["gu"], "down": m["down"]})
+            out.append(d)
+        return out
     for layer in layers:
         if not isinstance(layer.mlp, MLP):
             raise NotImplementedError("the graph path covers dense MLP layers")
@@ -80,7 +102,7 @@ class _Stack:
 
 
 def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
-                   mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True) -> int:
+                   mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True, tp=None) -> int:
     """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count."""
     Hq, Hkv, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
     scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
@@ -92,10 +114,16 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
         X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps, pdl=pdl)
         X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits, scale,
                                causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
-        X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
+        if tp is None:
+            X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
+        else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory
+            tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl)
         X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
         X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
-        X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
+        if tp is None:
+            X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
+        else:
+            tp.gemm_allreduce(st.act, L["down"], st.x, residual=st.x, pdl=pdl)
         n += 8 + (1 if st.splits > 1 else 0)
         if taps is not None and li != last:
             for j, t in enumerate(tap_ids):
@@ -121,7 +149,14 @@ class FastRound:
         X.load()
         m = engine.model
         self.embed_w, self.lm_head_w, self.final_norm = m.model.embed_tokens.weight, m.lm_head.weight, m.model.norm.weight
-        self.layers = kernel_layer_weights(m.model.layers)
+        self.tp = getattr(engine, "tp", None)
+        world = self.tp.world if self.tp is not None else 1
+        self.lcfg = local_dims(self.cfg, world)
+        self.layers = kernel_layer_weights(m.model.layers, self.cfg, self.tp)
+        if self.tp is not None:
+            from ..parallel.tp import shard_rows
+            self.vocab_local = self.cfg.vocab_size // world
+            self.lm_head_w = shard_rows(m.lm_head.weight, self.tp.rank, world)
         self.freq = X.inv_freq(self.cfg.head_dim, self.cfg.rope_theta, self.device)
         self.graphs: dict = {}
         self.draft_cache: dict = {}
@@ -184,9 +219,9 @@ class FastRound:
         eos = sorted(self.eng.eos_token_ids)
         r["eos"] = torch.tensor(eos or [-1], dtype=torch.int32, device=dev)
         r["n_eos"] = len(eos)
-        r["stack"] = _Stack(cfg, NB, dev, pool.max_seq_len)
+        r["stack"] = _Stack(self.lcfg, NB, dev, pool.max_seq_len)
         r["xn"] = torch.zeros(NB, H, dtype=torch.bfloat16, device=dev)
-        nt = X.n_tiles(cfg.vocab_size)
+        nt = X.n_tiles(self.lm_head_w.shape[0])
         r["am_ws"] = {"val": torch.zeros(NB, nt, dtype=torch.float32, device=dev),
                       "idx": torch.zeros(NB, nt, dtype=torch.int32, device=dev)}
         r["am_val"] = torch.zeros(NB, dtype=torch.float32, device=dev)
@@ -194,9 +229,14 @@ class FastRound:
         if head is not None:
             self._draft_buffers(r, head)
         # run every kernel once outside capture (module load, function attributes), then capture
+        if self.tp is not None:
+            self.tp.begin_sequence()
         r["launches"] = self._launch_round(r, pdl=False)
         torch.cuda.synchronize()
         X.status_word(dev).zero_()
+        if self.tp is not None:
+            self.tp.begin_sequence(self.tp._turn)     # cycle length that is safe across replays
+            r["ring_mod"] = self.tp.ring_mod
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._launch_round(r, pdl=_PDL)
@@ -296,9 +336,9 @@ class FastRound:
                                    p(r["slots"]), p(r["mask"]), p(status), int(pdl), s()), "js_tree_build")
         st = r["stack"]
         X.embed(r["tokens"], self.embed_w, out=st.x, pdl=pdl)
-        n += 2 + decoder_layers(cfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"], r["cu_q"],
-                                r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"], False,
-                                self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl)
+        n += 2 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
+                                r["cu_q"], r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"],
+                                False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp)
         X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
         last = cfg.num_hidden_layers - 1
         if r["taps"] is not None:
@@ -306,7 +346,11 @@ class FastRound:
                 if t == last:
                     X.gather_rows(r["xn"], None, r["taps"], dst_col0=j * cfg.hidden_size, pdl=pdl)
                     n += 1
-        X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        if self.tp is None:
+            X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        else:
+            self.tp.lm_head_argmax(r["xn"], self.lm_head_w, self.tp.rank * self.vocab_local, r["am_ws"], r["greedy"],
+                                   r["am_val"], pdl=pdl)
         X._check(lib.js_tree_accept_commit(p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["greedy"]), NB,
                                            p(r["state"]), p(pool.slot_map), p(r["seq_rows"]), pool.max_seq_len,
                                            p(r["committed"]), r["committed"].numel(), p(r["eos"]), r["n_eos"],
@@ -320,8 +364,11 @@ class FastRound:
         """Prefill through the eager kernel path and initialise the round's device state."""
         eng, pool = self.eng, self.eng.pool
         T = ids.shape[1]
-        logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
-        first = int(logits[-1].float().argmax())
+        if self.tp is None:
+            logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
+            first = int(logits[-1].float().argmax())
+        else:
+            first, hidden = self._prefill_kernels(sid, ids, taps, total)
         r["seq_rows"].fill_(pool.state(sid).row)
         state = torch.zeros(8, dtype=torch.int32)
         state[ST_PAST], state[ST_GEN] = T, 1
@@ -346,7 +393,51 @@ class FastRound:
             state[ST_CTX] = n
         r["state"].copy_(state)
         torch.cuda.synchronize()
+        if self.tp is not None:
+            self.tp.begin_sequence()      # the graph's collectives restart their buffer cycle here
+            self.tp.ring_mod = r.get("ring_mod", self.tp.ring_mod)
         return first
+
+    def _prefill_kernels(self, sid: int, ids: torch.Tensor, taps, total: int):
+        """Causal prefill on the kernel path in chunks (the tensor-parallel route: sharded weights,
+        fused GEMM+all-reduce).  Returns ``(first greedy token, tapped hidden (T, taps*H) or None)``."""
+        pool, dev, cfg = self.eng.pool, self.device, self.cfg
+        T, H = ids.shape[1], cfg.hidden_size
+        pool.reserve(sid, total)
+        row = pool.state(sid).row
+        chunk = 512 if self.tp is None else min(512, self.tp.m_cap)
+        tap_ids = list(taps) if taps else None
+        hidden = torch.empty(T, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
+        seq_rows = torch.tensor([row], dtype=torch.int32, device=dev)
+        ids32 = ids[0].to(device=dev, dtype=torch.int32)
+        last = cfg.num_hidden_layers - 1
+        xn = None
+        for s0 in range(0, T, chunk):
+            n = min(chunk, T - s0)
+            st = _Stack(self.lcfg, n, dev, pool.max_seq_len)
+            pos = torch.arange(s0, s0 + n, dtype=torch.int32, device=dev)
+            slots = pool.slot_map[row, s0:s0 + n].contiguous()
+            cu_q = torch.tensor([0, n], dtype=torch.int32, device=dev)
+            past = torch.tensor([s0], dtype=torch.int32, device=dev)
+            tapbuf = hidden[s0:s0 + n] if hidden is not None else None
+            X.embed(ids32[s0:s0 + n].contiguous(), self.embed_w, out=st.x)
+            decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, seq_rows, cu_q, past,
+                           pos, slots, None, True, self.freq, taps=tapbuf, tap_ids=tap_ids, pdl=False, tp=self.tp)
+            xn = X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps)
+            if tap_ids:
+                for j, t in enumerate(tap_ids):
+                    if t == last:
+                        hidden[s0:s0 + n, j * H:(j + 1) * H] = xn
+        h_last = xn[-1:].contiguous()
+        out_idx = torch.empty(1, dtype=torch.int32, device=dev)
+        nt = X.n_tiles(self.lm_head_w.shape[0])
+        ws = {"val": torch.empty(1, nt, dtype=torch.float32, device=dev), "idx": torch.empty(1, nt, dtype=torch.int32, device=dev)}
+        if self.tp is None:
+            X.lm_head_argmax(h_last, self.lm_head_w, ws=ws, out_idx=out_idx)
+        else:
+            self.tp.lm_head_argmax(h_last, self.lm_head_w, self.tp.rank * self.vocab_local, ws, out_idx)
+        pool.state(sid).length = T
+        return int(out_idx.item()), hidden
 
     # ------------------------------------------------------------------ public entry points
     @torch.inference_mode()

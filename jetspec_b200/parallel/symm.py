@@ -1,0 +1,59 @@
+"""Peer-visible ("symmetric") device buffers.
+
+Each rank allocates the same-sized buffer with the kernel library's allocator, the CUDA
+IPC handles travel through the host process group, and every rank maps all peers'
+buffers.  ``ptrs_dev`` is a device array of ``world`` addresses (this rank's own buffer at
+index ``rank``) that the fused compute+collective kernels index by rank; they reach peer
+memory with plain loads and stores over NVLink.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+
+class SymmetricBuffer:
+    def __init__(self, nbytes: int, group=None):
+        import torch.distributed as dist
+        from ..ops import cuda_ext as X
+        lib = X.load()
+        lib.js_symm_alloc.restype = ctypes.c_void_p
+        lib.js_symm_alloc.argtypes = [ctypes.c_size_t]
+        lib.js_symm_import.restype = ctypes.c_void_p
+        lib.js_symm_export.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+        lib.js_symm_free.argtypes = [ctypes.c_void_p]
+        lib.js_symm_unmap.argtypes = [ctypes.c_void_p]
+        self._lib = lib
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.nbytes = int(nbytes)
+        self.local = lib.js_symm_alloc(self.nbytes)
+        if not self.local:
+            raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed")
+        handle = ctypes.create_string_buffer(64)
+        if lib.js_symm_export(ctypes.c_void_p(self.local), handle) != 0:
+            raise RuntimeError("cudaIpcGetMemHandle failed")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.local)
+            else:
+                p = lib.js_symm_import(ctypes.c_char_p(h))
+                if not p:
+                    raise RuntimeError(f"mapping rank {r}'s buffer failed (cudaIpcOpenMemHandle)")
+                self.ptrs.append(p)
+        self.ptrs_dev = torch.tensor(self.ptrs, dtype=torch.int64, device="cuda")
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank and p:
+                self._lib.js_symm_unmap(ctypes.c_void_p(p))
+        if self.local:
+            self._lib.js_symm_free(ctypes.c_void_p(self.local))
+        self.ptrs, self.local = [], None

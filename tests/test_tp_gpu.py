@@ -1,0 +1,34 @@
+"""Multi-GPU gates: fused GEMM+all-reduce and TP argmax against NCCL twins, TP engine losslessness."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(nproc: int, *args, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "tp_worker.py"), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    return r.returncode, r.stdout + r.stderr
+
+
+def test_fused_collectives_two_ranks():
+    rc, out = _launch(2)
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+def test_tp_engine_two_ranks():
+    rc, out = _launch(2, "engine")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_tp_engine_four_ranks():
+    rc, out = _launch(4, "engine")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]

@@ -1,0 +1,95 @@
+"""Worker for the multi-GPU tests (launched by torch.distributed.run, one rank per GPU).
+
+Checks the fused row-parallel GEMM + all-reduce and the vocabulary-parallel argmax against their
+unfused NCCL twins, then (optionally) a tensor-parallel tree decode against the single-GPU engine.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    from jetspec_b200.ops import cuda_ext as X
+    from jetspec_b200.parallel import TensorParallel, shard_cols, shard_rows
+    X.load()
+    tp = TensorParallel(None, m_cap=512, n_max=4096)
+    g = torch.Generator(device="cuda").manual_seed(0)       # same seed: every rank builds the full tensors
+    ok = True
+    for (M, N, K) in [(128, 4096, 4096), (21, 1024, 2048), (300, 512, 1024), (1, 4096, 12288)]:
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+        res = torch.randn(M, N, generator=g, device="cuda").to(torch.bfloat16)
+        xl, wl = shard_cols(x, rank, world), shard_cols(w, rank, world)
+        for rep in range(6):                                 # several turns of the buffer ring
+            out = res.clone()
+            tp.gemm_allreduce(xl, wl, out, residual=out)
+            torch.cuda.synchronize()
+        ref = x.float() @ w.float().t() + res.float()
+        err = float((out.float() - ref).abs().max() / ref.abs().max())
+        base = torch.empty_like(res)
+        tp.gemm_allreduce_nccl(xl, wl, base, residual=res)
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(gathered[0], t) for t in gathered)      # replicas must be bit-identical
+        if rank == 0:
+            print(f"gemm_allreduce M={M} N={N} K={K}: rel err {err:.2e}, replicas identical {same}", flush=True)
+        ok &= err < 1.5e-2 and same
+    # vocabulary-parallel argmax
+    M, V, H = 128, 8192, 512
+    h = torch.randn(M, H, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(V, H, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    wl = shard_rows(w, rank, world)
+    nt = X.n_tiles(wl.shape[0])
+    ws = {"val": torch.empty(M, nt, dtype=torch.float32, device="cuda"), "idx": torch.empty(M, nt, dtype=torch.int32, device="cuda")}
+    out_idx = torch.empty(M, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        tp.lm_head_argmax(h, wl, rank * (V // world), ws, out_idx)
+        torch.cuda.synchronize()
+    logits = h.float() @ w.float().t()
+    chosen = logits.gather(1, out_idx.long()[:, None]).squeeze(1)
+    gap = float((logits.max(-1).values - chosen).max())
+    if rank == 0:
+        print(f"tp argmax: worst shortfall {gap:.3e}", flush=True)
+    ok &= gap < 0.05
+    X.check_status("cuda")
+    if len(sys.argv) > 1 and sys.argv[1] == "engine":
+        ok &= engine_check(tp, rank, world)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_WORKER_OK" if int(flag) == 1 else "TP_WORKER_FAILED", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 1 else 1)
+
+
+def engine_check(tp, rank, world) -> bool:
+    from jetspec_b200 import JetSpecEngine, SamplingParams, OracleTreeDrafter
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    cfg = Qwen3Config(vocab_size=8192, hidden_size=1024, intermediate_size=2048, num_hidden_layers=4,
+                      num_attention_heads=8, num_key_value_heads=8, head_dim=128)
+    model = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda", init="stable")
+    prompt = torch.randint(0, cfg.vocab_size, (1, 40), generator=torch.Generator().manual_seed(0))
+    sp = SamplingParams(0.0, 48)
+    eng = JetSpecEngine(model, device=f"cuda:{torch.cuda.current_device()}", dtype=torch.bfloat16, max_seq_len=512,
+                        tensor_parallel=tp)
+    ar = eng.generate(prompt, sp)["token_ids"]
+    expect = [(int(prompt[0, -1]) + 1 + i) % cfg.vocab_size for i in range(48)]   # the stable init counts upwards
+    oracle = OracleTreeDrafter(prompt[0].tolist() + ar, cfg.vocab_size, tree_width=4, mean_accept=3.0, max_accept=7, seed=1)
+    out = eng.generate_tree(prompt, oracle, tree_depth=8, tree_width=4, budget=32, sampling_params=sp, return_stats=True)
+    good = ar == expect and out["token_ids"] == expect and out["tpf"] > 2.0
+    if rank == 0:
+        print(f"tp engine: AR ok {ar == expect}, tree ok {out['token_ids'] == expect}, tokens/round {out['tpf']:.2f}", flush=True)
+    return good
+
+
+if __name__ == "__main__":
+    main()
