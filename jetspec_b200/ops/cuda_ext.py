@@ -331,9 +331,11 @@ def gather_rows(src: torch.Tensor, idx: Optional[torch.Tensor], dst: torch.Tenso
 
 # ------------------------------------------------------------------ attention
 def attn_splits(q_tiles: int, Hkv: int, max_keys: int) -> int:
-    ctas = max(1, q_tiles * Hkv)
-    want = max(1, (2 * SM_COUNT + ctas - 1) // ctas)
-    return max(1, min(want, (max_keys + 255) // 256, 16))
+    # the launcher adds one q tile per sequence for raggedness; keep the whole grid in ONE wave
+    # (two CTAs fit per SM) and give every split at least a couple of key tiles
+    ctas = max(1, (q_tiles + 1) * Hkv)
+    want = max(1, (2 * SM_COUNT) // ctas)
+    return max(1, min(want, (max_keys + 127) // 128, 16))
 
 
 def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens, mask_bits, scale: float,
