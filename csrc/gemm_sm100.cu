@@ -32,7 +32,7 @@ constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kTopK = 8;
 
-enum GemmEpi : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_TOPK = 3, EPI_STORE_F32 = 4, EPI_ALLREDUCE = 5 };
+enum GemmEpi : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_TOPK = 3, EPI_STORE_F32 = 4, EPI_ALLREDUCE = 5, EPI_EP_COMBINE = 6 };
 
 struct GemmParams {
   int M, N, K;
@@ -48,6 +48,16 @@ struct GemmParams {
   __nv_bfloat16* const* peer_recv;  // [world] -> (world, m_cap, N) bf16 on that rank
   int* const* peer_flags;           // [world] -> one counter per CTA of this grid on that rank
   int rank, world, m_cap;
+  // grouped mode (MoE experts): blockIdx.z is the expert; its rows are group_off[e] .. group_off[e+1]
+  // of A and C, its weights are rows e*N .. (e+1)*N of W.  No K split in this mode.
+  const int* group_off;
+  // EPI_EP_COMBINE (expert-parallel down projection): row r of the sorted rows belongs to
+  // (token, choice) pair row_pair[r] with routing weight row_weight[r]; the weighted output row is
+  // stored into every rank's pair buffer (n_pairs, N) and a per-rank counter is bumped per CTA.
+  const int* row_pair;
+  const float* row_weight;
+  __nv_bfloat16* const* peer_pairs;
+  int* const* peer_cnt;
 };
 
 JS_DEVICE void red_release_sys_add(int* addr, int v) {
@@ -106,7 +116,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // [pipeline stages][split-K receive area][barriers]; the receive area is separate from the
   // stages because peers push into it while this CTA may still be streaming
-  const int data_bytes = S::kTiles + recv_bytes(gridDim.z, BN, EPI == EPI_SWIGLU);
+  const bool grouped = p.group_off != nullptr;
+  const int data_bytes = S::kTiles + recv_bytes(grouped ? 1 : gridDim.z, BN, EPI == EPI_SWIGLU);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + data_bytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* accum_bar = empty_bar + kStages;
@@ -114,10 +125,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int split = gridDim.z;
-  const int z = blockIdx.z;                  // == rank in the (1,1,split) cluster
+  const int split = grouped ? 1 : gridDim.z;
+  const int z = grouped ? 0 : blockIdx.z;    // == rank in the (1,1,split) cluster
+  const int expert = grouped ? blockIdx.z : 0;
   const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * BM;
+  const int m0 = grouped ? p.group_off[expert] + blockIdx.y * BM : blockIdx.y * BM;
+  const int m_end = grouped ? p.group_off[expert + 1] : p.M;
+  const int wn0 = expert * p.N + n0;         // row of this tile in the (stacked) weight matrix
+  if (m0 >= m_end) return;                   // this expert has fewer row tiles (uniform for the CTA)
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_begin = (kb_total * z) / split;
   const int kb_end = (kb_total * (z + 1)) / split;
@@ -154,7 +169,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int pre = nkb < kStages ? nkb : kStages;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], S::kStage);
-        tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * BK, n0);
+        tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * BK, wn0);
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i)
@@ -164,7 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t ph = (i / kStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) break;
         mbar_expect_tx(&full_bar[s], S::kStage);
-        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * BK, n0);
+        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * BK, wn0);
         tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * BK, m0);
       }
     }
@@ -260,7 +275,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     };
 
-    if constexpr (EPI == EPI_ALLREDUCE) {
+    if constexpr (EPI == EPI_EP_COMBINE) {
+      // Expert-parallel combine fused into the experts' down projection: each output row is scaled
+      // by its routing weight and stored into every rank's (token, choice) pair buffer over NVLink;
+      // one release-increment per CTA and rank lets the finishing kernel know when all experts of
+      // all ranks have delivered.
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        load_chunk(c0, v);
+        const int gc = n0 + c0;
+        if (grow < m_end && gc < p.N) {
+          const float wgt = p.row_weight[grow];
+          const size_t off = static_cast<size_t>(p.row_pair[grow]) * p.N + gc;
+          uint4 pk[4];
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(pk);
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o2[t] = __floats2bfloat162_rn(v[2 * t] * wgt, v[2 * t + 1] * wgt);
+          for (int r = 0; r < p.world; ++r) {
+            uint4* dst = reinterpret_cast<uint4*>(p.peer_pairs[r] + off);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (gc + 8 * t < p.N) dst[t] = pk[t];
+          }
+        }
+      }
+      __threadfence_system();
+      epi_barrier();
+      if (threadIdx.x == 64)
+        for (int r = 0; r < p.world; ++r) red_release_sys_add(p.peer_cnt[r], 1);
+    } else if constexpr (EPI == EPI_ALLREDUCE) {
       // Row-parallel GEMM fused with the tensor-parallel all-reduce (one shot): each finished
       // 32-column chunk of this rank's partial product is stored as bf16 straight into every
       // rank's receive buffer over NVLink, a per-CTA counter on each rank is bumped with release
@@ -356,7 +399,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         float v[32];
         load_chunk(c0, v);
         const int gc = n0 + c0;
-        if (grow < p.M && gc < p.N) {
+        if (grow < m_end && gc < p.N) {
           if constexpr (EPI == EPI_STORE_F32) {
             float* out = reinterpret_cast<float*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
 #pragma unroll
@@ -394,7 +437,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         load_chunk(c0, g);
         load_chunk(HALF + c0, u);
         const int gc = n0 / 2 + c0;              // output column
-        if (grow < p.M && gc < p.N / 2) {
+        if (grow < m_end && gc < p.N / 2) {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(grow) * p.ldc + gc;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -508,7 +551,7 @@ static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t col
 
 template <int BN, int EPI, int BUDGET_KB>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int groups = 0, int group_m_tiles = 0) {
   using S = GemmSmem<BN, BUDGET_KB>;
   static int configured = 0;
   auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB>;
@@ -520,6 +563,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
+  if (groups > 0) cfg.gridDim = dim3((p.N + BN - 1) / BN, group_m_tiles, groups);   // z = expert, no K split
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
@@ -562,7 +606,7 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   CUtensorMap ta, tw;
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, bn)) return -16;
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace,
-               nullptr, nullptr, 0, 1, 0};
+               nullptr, nullptr, 0, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr};
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
     return (split > 1 && BN_ < 256) ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
@@ -598,7 +642,38 @@ extern "C" int js_gemm_bf16_allreduce(const void* A, const void* W, void* C, con
   CUtensorMap ta, tw;
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, 128)) return -16;
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), nullptr, nullptr, nullptr, status,
-               nullptr, reinterpret_cast<__nv_bfloat16* const*>(peer_recv), peer_flags, rank, world, m_cap};
+               nullptr, reinterpret_cast<__nv_bfloat16* const*>(peer_recv), peer_flags, rank, world, m_cap,
+               nullptr, nullptr, nullptr, nullptr, nullptr};
   return split > 1 ? launch_gemm<128, EPI_ALLREDUCE, 128>(ta, tw, p, split, pdl != 0, stream)
                    : launch_gemm<128, EPI_ALLREDUCE, 96>(ta, tw, p, split, pdl != 0, stream);
+}
+
+// Grouped GEMM over `groups` experts in one launch.  A (total_rows, K) holds the rows sorted by expert,
+// expert e owning rows group_off[e] .. group_off[e+1] (device array, groups+1 entries); W is the stacked
+// (groups*N, K) weight; C (total_rows, N or N/2).  epi: 0 store, 1 swiglu (per-expert tile-interleaved
+// gate/up), 6 expert-parallel combine (weighted rows pushed to every rank's pair buffer).
+// max_rows_per_group bounds the row tiles launched per expert.
+extern "C" int js_gemm_bf16_grouped(const void* A, const void* W, void* C, int total_rows, int N, int K, int lda,
+                                    int ldw, int ldc, int epi, int groups, const int* group_off,
+                                    int max_rows_per_group, const int* row_pair, const float* row_weight,
+                                    void* const* peer_pairs, int* const* peer_cnt, int world, int* status, int pdl,
+                                    cudaStream_t stream) {
+  using namespace js;
+  if (total_rows <= 0 || groups <= 0) return 0;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (N % 128)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
+  CUtensorMap ta, tw;
+  if (make_map(&ta, A, total_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128)) return -16;
+  GemmParams p{total_rows, N, K, ldc, C, nullptr, nullptr, nullptr, nullptr, status, nullptr,
+               nullptr, nullptr, 0, world, 0, group_off, row_pair, row_weight,
+               reinterpret_cast<__nv_bfloat16* const*>(peer_pairs), peer_cnt};
+  const int m_tiles = (max_rows_per_group + BM - 1) / BM;
+  if (m_tiles < 1) return 0;
+  if (epi == EPI_STORE) return launch_gemm<128, EPI_STORE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+  if (epi == EPI_SWIGLU) return launch_gemm<128, EPI_SWIGLU, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+  if (epi == EPI_EP_COMBINE) {
+    if (!row_pair || !row_weight || !peer_pairs || !peer_cnt) return -22;
+    return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+  }
+  return -17;
 }

@@ -371,29 +371,38 @@ def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
 
 
 # ------------------------------------------------------------------ MoE (grouped through the dense GEMM)
+_moe_cache: dict = {}
+
+
 def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_logits=None):
-    """Sparse MoE on one GPU: route, sort tokens by expert, run each expert's SwiGLU MLP on its
-    contiguous rows with the tcgen05 GEMM, combine with the routing weights."""
+    """Sparse MoE on one GPU: route, sort the (token, choice) pairs by expert, run all experts'
+    SwiGLU MLPs with two grouped tcgen05 GEMMs (one launch each), combine with the routing weights."""
     from . import reference as ref
+    from ..parallel.ep import interleave_experts, route_and_sort
+    lib = load()
     T, H = x.shape
     E, I2, _ = w_gate_up.shape
+    I = I2 // 2
+    if I % 64 or H % 128:
+        return ref.moe_forward(x, gate_w, w_gate_up, w_down, top_k, renorm, router_logits)
+    key = (w_gate_up.data_ptr(), w_down.data_ptr())
+    if key not in _moe_cache:
+        _moe_cache[key] = (interleave_experts(w_gate_up), w_down.reshape(E * H, I).contiguous())
+    gu, dn = _moe_cache[key]
     if router_logits is None:
         router_logits = gemm(x, gate_w, epi=EPI_STORE_F32) if gemm_supported(T, E, H) else torch.nn.functional.linear(x, gate_w)
-    wts, idx = ref.moe_route(router_logits, top_k, renorm)
-    flat_e = idx.reshape(-1)
-    order = torch.argsort(flat_e, stable=True)
-    tok = torch.arange(T, device=x.device).repeat_interleave(top_k)[order]
-    counts = torch.bincount(flat_e, minlength=E).tolist()
-    xs = x[tok].contiguous()
-    ys = torch.empty(xs.shape[0], H, dtype=x.dtype, device=x.device)
-    s = 0
-    for e, c in enumerate(counts):
-        if c == 0:
-            continue
-        h = gemm(xs[s:s + c], w_gate_up[e])
-        h = silu_mul(h)
-        gemm(h, w_down[e], out=ys[s:s + c])
-        s += c
+    order, row_w, group_off, _ = route_and_sort(router_logits, top_k, renorm, 0, E)
+    tok = torch.div(order, top_k, rounding_mode="floor")
+    xs = x.index_select(0, tok)
+    h = torch.empty(T * top_k, I, dtype=x.dtype, device=x.device)
+    ys = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
+    st = _p(status_word(x.device))
+    _check(lib.js_gemm_bf16_grouped(_p(xs), _p(gu), _p(h), T * top_k, 2 * I, H, xs.stride(0), gu.stride(0), h.stride(0),
+                                    EPI_SWIGLU, E, _p(group_off), T, None, None, None, None, 1, st, 0, _stream()),
+           "grouped gate/up")
+    _check(lib.js_gemm_bf16_grouped(_p(h), _p(dn), _p(ys), T * top_k, H, I, h.stride(0), dn.stride(0), ys.stride(0),
+                                    EPI_STORE, E, _p(group_off), T, None, None, None, None, 1, st, 0, _stream()),
+           "grouped down")
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    out.index_add_(0, tok, ys.float() * wts.reshape(-1)[order, None])
+    out.index_add_(0, tok, ys.float() * row_w[:, None])
     return out.to(x.dtype)

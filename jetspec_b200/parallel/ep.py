@@ -1,0 +1,139 @@
+"""Expert parallelism for Qwen3-MoE layers.
+
+The residual stream is replicated on every rank (as in the tensor-parallel plan), so *dispatch*
+needs no communication: each rank routes all tokens (the router is tiny and replicated) and
+gathers the (token, choice) pairs whose expert it owns.  One grouped tcgen05 GEMM runs the
+experts' gate/up projections with the SwiGLU epilogue; a second grouped GEMM runs the down
+projections and its epilogue IS the *combine*: every output row is scaled by its routing weight
+and stored straight into all ranks' pair buffers over NVLink, one counter per rank is bumped per
+CTA, and a finishing kernel on each rank waits for the global count and sums the ``top_k`` rows of
+every token in choice order (bit-identical replicas, no atomics).
+
+Reference behaviour of the layer itself: ``jetspec/models/moe_fused.py:16-51`` (softmax top-k
+routing, sort by expert, two grouped GEMMs, weighted un-sort).  The reference has no expert
+parallelism; the measured baseline is :meth:`ExpertParallel.moe_layer_nccl` (library grouped math
++ NCCL all-reduce).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import reference as ref
+from .symm import SymmetricBuffer
+
+
+def interleave_experts(w_gate_up: torch.Tensor, bn: int = 128) -> torch.Tensor:
+    """``(E, 2I, H)`` stacked ``[gate | up]`` → ``(E*2I, H)`` with every ``bn``-row tile holding
+    ``bn/2`` gate rows then the ``bn/2`` up rows of the same outputs (the SwiGLU epilogue's layout)."""
+    E, I2, H = w_gate_up.shape
+    I, h = I2 // 2, bn // 2
+    g = w_gate_up[:, :I].reshape(E, I // h, h, H)
+    u = w_gate_up[:, I:].reshape(E, I // h, h, H)
+    return torch.cat((g, u), dim=2).reshape(E * I2, H).contiguous()
+
+
+def route_and_sort(router_logits: torch.Tensor, top_k: int, renorm: bool, first_expert: int, n_local: int):
+    """Routing plus the static-shape permutation used by the grouped GEMMs.
+
+    Returns ``(order, row_weight, group_off, counts_all)``: ``order (T*k,)`` lists pair indices
+    ``t*k+j`` sorted by local expert (pairs of other ranks' experts last), ``row_weight`` their routing
+    weights, ``group_off (n_local+1,)`` the row ranges of the local experts, ``counts_all (E,)`` the
+    global per-expert pair counts (identical on every rank).
+    """
+    wts, idx = ref.moe_route(router_logits, top_k, renorm)
+    E = router_logits.shape[-1]
+    flat_e = idx.reshape(-1)
+    local = flat_e - first_expert
+    key = torch.where((local >= 0) & (local < n_local), local, torch.full_like(local, n_local))
+    order = torch.argsort(key, stable=True)
+    counts_local = torch.bincount(key, minlength=n_local + 1)[:n_local]
+    group_off = torch.zeros(n_local + 1, dtype=torch.int32, device=router_logits.device)
+    group_off[1:] = torch.cumsum(counts_local, 0).to(torch.int32)
+    counts_all = torch.bincount(flat_e, minlength=E)
+    return order, wts.reshape(-1)[order].float().contiguous(), group_off, counts_all
+
+
+class ExpertParallel:
+    RING = 3
+
+    def __init__(self, group, num_experts: int, top_k: int, hidden: int, max_tokens: int):
+        import torch.distributed as dist
+        from ..ops import cuda_ext as X
+        self._X = X
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        assert num_experts % self.world == 0
+        self.E, self.k, self.H, self.max_tokens = num_experts, top_k, hidden, max_tokens
+        self.n_local = num_experts // self.world
+        self.first = self.rank * self.n_local
+        self.pairs = [SymmetricBuffer(max_tokens * top_k * hidden * 2, group) for _ in range(self.RING)]
+        self.cnt = [SymmetricBuffer(64, group) for _ in range(self.RING)]
+        self.done = torch.zeros(self.RING, dtype=torch.int32, device="cuda")
+        self._turn = 0
+        self.launches = 0
+
+    def shard(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+        """This rank's experts as the two stacked kernel operands."""
+        gu = interleave_experts(w_gate_up[self.first:self.first + self.n_local])
+        dn = w_down[self.first:self.first + self.n_local]
+        return gu, dn.reshape(self.n_local * dn.shape[1], dn.shape[2]).contiguous()
+
+    def moe_layer(self, x: torch.Tensor, gate_w: torch.Tensor, gu_local: torch.Tensor, down_local: torch.Tensor,
+                  renorm: bool, out: Optional[torch.Tensor] = None, router_logits: Optional[torch.Tensor] = None,
+                  pdl: bool = False) -> torch.Tensor:
+        """``out = x + MoE(x)`` with expert-parallel experts; ``x (T, H)`` replicated on every rank."""
+        X = self._X
+        lib = X.load()
+        T, H = x.shape
+        I = gu_local.shape[0] // (2 * self.n_local)
+        assert T <= self.max_tokens and H == self.H
+        if router_logits is None:
+            router_logits = X.gemm(x, gate_w, epi=X.EPI_STORE_F32)
+        order, row_w, group_off, counts_all = route_and_sort(router_logits, self.k, renorm, self.first, self.n_local)
+        tok = torch.div(order, self.k, rounding_mode="floor")
+        xs = x.index_select(0, tok)                                   # (T*k, H); rows past the local groups are unused
+        h = torch.empty(T * self.k, I, dtype=x.dtype, device=x.device)
+        st = X._p(X.status_word(x.device))
+        X._check(lib.js_gemm_bf16_grouped(X._p(xs), X._p(gu_local), X._p(h), T * self.k, 2 * I, H, xs.stride(0),
+                                          gu_local.stride(0), h.stride(0), X.EPI_SWIGLU, self.n_local, X._p(group_off),
+                                          T, None, None, None, None, 1, st, int(pdl), X._stream()), "grouped gate/up")
+        t = self._turn % self.RING
+        self._turn += 1
+        row_pair = order.to(torch.int32).contiguous()
+        X._check(lib.js_gemm_bf16_grouped(X._p(h), X._p(down_local), None, T * self.k, H, I, h.stride(0),
+                                          down_local.stride(0), H, 6, self.n_local, X._p(group_off), T, X._p(row_pair),
+                                          X._p(row_w), X._p(self.pairs[t].ptrs_dev), X._p(self.cnt[t].ptrs_dev),
+                                          self.world, st, int(pdl), X._stream()), "grouped down + combine")
+        # every rank knows all experts' loads, hence how many CTAs of all ranks will report in
+        expected = (torch.div(counts_all + 127, 128, rounding_mode="floor").sum() * (H // 128)).to(torch.int32).reshape(1)
+        if out is None:
+            out = torch.empty_like(x)
+        import ctypes
+        X._check(lib.js_ep_combine_finish(ctypes.c_void_p(self.pairs[t].local), ctypes.c_void_p(self.cnt[t].local),
+                                          X._p(expected), X._p(self.done[t:t + 1]), X._p(x), X._p(out), T, self.k, H, st,
+                                          int(pdl), X._stream()), "ep combine finish")
+        self.launches += 3
+        return out
+
+    def moe_layer_nccl(self, x, gate_w, w_gate_up, w_down, renorm, router_logits=None):
+        """Unfused baseline twin: this rank's experts through plain PyTorch, NCCL all-reduce, residual."""
+        import torch.distributed as dist
+        if router_logits is None:
+            router_logits = torch.nn.functional.linear(x, gate_w)
+        wts, idx = ref.moe_route(router_logits, self.k, renorm)
+        part = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        flat_e, flat_w = idx.reshape(-1), wts.reshape(-1)
+        flat_t = torch.arange(x.shape[0], device=x.device).repeat_interleave(self.k)
+        for e in range(self.first, self.first + self.n_local):
+            sel = (flat_e == e).nonzero(as_tuple=True)[0]
+            if sel.numel():
+                hh = ref.silu_mul(torch.nn.functional.linear(x[flat_t[sel]], w_gate_up[e]))
+                part.index_add_(0, flat_t[sel], torch.nn.functional.linear(hh, w_down[e]).float() * flat_w[sel, None])
+        dist.all_reduce(part, group=self.group)
+        return (x.float() + part).to(x.dtype)
+
+    def close(self):
+        for b in self.pairs + self.cnt:
+            b.close()

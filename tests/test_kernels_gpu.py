@@ -238,3 +238,18 @@ def test_device_tree_build_and_accept_match_host(ext, seed):
     assert win_after[:acc_h + 1].tolist() == win_before[path_h].tolist()
     assert torch.equal(slot_row[:past], slot_before[:past]) and torch.equal(slot_row[past + NB:], slot_before[past + NB:])
     ext.check_status(dev)
+
+
+@pytest.mark.parametrize("T", [5, 200])
+def test_grouped_moe_matches_reference(ext, T):
+    from jetspec_b200.ops import reference as ref
+    E, H, I, k = 16, 256, 128, 4
+    x = rnd(T, H, seed=30)
+    gate = rnd(E, H, scale=0.5, seed=31)
+    wgu, wd = rnd(E, 2 * I, H, scale=0.06, seed=32), rnd(E, H, I, scale=0.06, seed=33)
+    logits = (x.float() @ gate.float().t())            # same routing for both sides
+    out = ext.moe_forward(x, gate, wgu, wd, k, True, router_logits=logits)
+    exp = ref.moe_forward(x.float(), gate.float(), wgu.float(), wd.float(), k, True, router_logits=logits)
+    torch.cuda.synchronize()
+    assert rel_err(out, exp) < 2 * BF16_TOL
+    ext.check_status("cuda")

@@ -59,6 +59,7 @@ def main():
     if rank == 0:
         print(f"tp argmax: worst shortfall {gap:.3e}", flush=True)
     ok &= gap < 0.05
+    ok &= ep_check(rank, world)
     X.check_status("cuda")
     if len(sys.argv) > 1 and sys.argv[1] == "engine":
         ok &= engine_check(tp, rank, world)
@@ -69,6 +70,34 @@ def main():
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if int(flag) == 1 else 1)
+
+
+def ep_check(rank, world) -> bool:
+    """Fused expert-parallel MoE layer against its NCCL twin and the single-device reference."""
+    from jetspec_b200.parallel.ep import ExpertParallel
+    from jetspec_b200.ops import reference as ref
+    E, H, I, k, T = 16, 512, 128, 4, 96
+    g = torch.Generator(device="cuda").manual_seed(7)
+    bf = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device="cuda") * sc).to(torch.bfloat16)
+    x, gate = bf(T, H), bf(E, H, sc=0.5)
+    wgu, wd = bf(E, 2 * I, H, sc=0.06), bf(E, H, I, sc=0.06)
+    logits = x.float() @ gate.float().t()
+    ep = ExpertParallel(None, E, k, H, max_tokens=128)
+    gu_l, dn_l = ep.shard(wgu, wd)
+    good = True
+    for _ in range(4):                                   # several turns of the buffer ring
+        out = ep.moe_layer(x, gate, gu_l, dn_l, True, router_logits=logits)
+        torch.cuda.synchronize()
+    exp = x.float() + ref.moe_forward(x.float(), gate.float(), wgu.float(), wd.float(), k, True, router_logits=logits)
+    base = ep.moe_layer_nccl(x, gate, wgu, wd, True, router_logits=logits)
+    err = float((out.float() - exp).abs().max() / exp.abs().max())
+    err_b = float((base.float() - exp).abs().max() / exp.abs().max())
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    same = all(torch.equal(gathered[0], t) for t in gathered)
+    if rank == 0:
+        print(f"ep moe layer: rel err {err:.2e} (nccl twin {err_b:.2e}), replicas identical {same}", flush=True)
+    return err < 2e-2 and same
 
 
 def engine_check(tp, rank, world) -> bool:
