@@ -22,6 +22,8 @@ _LAZY = {
     "DraftHeadDrafter": "jetspec_b200.drafters",
     "DraftHeadTreeDrafter": "jetspec_b200.drafters",
     "OracleTreeDrafter": "jetspec_b200.drafters",
+    "GraphedDraftHead": "jetspec_b200.drafters",
+    "CompiledDraftHead": "jetspec_b200.drafters",
     "OracleOverrideDrafter": "jetspec_b200.drafters",
     "load_draft_head": "jetspec_b200.models",
     "load_target": "jetspec_b200.models",

@@ -117,3 +117,29 @@ class DraftHeadTreeDrafter(_HeadDrafterMixin, TreeDrafter):
         """``(tokens (depth, width), logprobs (depth, width))`` with full-vocabulary log-probs."""
         rows = self._fwd.hidden_rows(context_ids, target_hidden)[:depth].contiguous()
         return ops.lm_head_topk_logprobs(rows, self._fwd.lm_head_w, width)
+
+
+class GraphedDraftHead(DraftHeadTreeDrafter):
+    """Draft head whose step is replayed from a CUDA graph.
+
+    In the reference this is a separate wrapper that owns one graph per context bucket and
+    recomputes the padded context every round (``jetspec/draft_head_adapter.py:446-602``).  Here the
+    engine's kernel path already captures the head's step inside the round's graph and extends a
+    persistent context K/V cache, so this class only marks the intent: handing it to
+    ``JetSpecEngine.generate_tree`` on a GPU selects the in-graph head; on CPU it behaves as the
+    eager :class:`DraftHeadTreeDrafter`.  ``propose`` gives the chain (argmax) view.
+    """
+
+    @torch.inference_mode()
+    def propose(self, context_ids, k, target_hidden=None, **kwargs):
+        return self.propose_logits(context_ids, k, target_hidden=target_hidden)[0].argmax(-1)
+
+    def clone(self) -> "GraphedDraftHead":
+        """A drafter sharing the weights but with its own context cache (one per sequence in a batch)."""
+        return type(self)(self.head, self.target, self.block_size, self.target_layer_ids, self.draft_shift)
+
+
+class CompiledDraftHead(GraphedDraftHead):
+    """Name kept for API parity with the reference's ``torch.compile`` variant
+    (``jetspec/draft_head_adapter.py:225-443``); there is no tracing compiler here, the kernels are
+    the same hand-written ones."""
