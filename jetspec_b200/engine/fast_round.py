@@ -186,10 +186,11 @@ class FastRound:
 
     # ------------------------------------------------------------------ buffers + capture
     def _round(self, NB: int, D: int, K: int, budget: int, head: Optional[DraftHeadTreeDrafter], staged: bool,
-               tap_ids, max_new: int):
+               tap_ids, max_new: int, remote=None):
         pool = self.eng.pool
-        tap_ids = list(tap_ids) if (tap_ids and head is not None) else None
-        key = (NB, D, K, budget, id(head) if head is not None else 0, staged, tuple(tap_ids or ()), id(pool))
+        tap_ids = list(tap_ids) if (tap_ids and (head is not None or remote is not None)) else None
+        key = (NB, D, K, budget, id(head) if head is not None else 0, staged, tuple(tap_ids or ()), id(pool),
+               id(remote) if remote is not None else 0)
         if key in self.graphs:
             return self.graphs[key]
         if pool.resident():
@@ -199,7 +200,7 @@ class FastRound:
         words = max(1, (NB + 31) // 32)
         Dn, Kn = max(1, D), max(1, K)
         r = {"NB": NB, "D": D, "K": K, "W": words, "budget": budget, "head": head, "staged": staged,
-             "max_new": 1 << 30, "tap_ids": tap_ids}
+             "max_new": 1 << 30, "tap_ids": tap_ids, "remote": remote}
         r["state"] = _i32(8, dev)
         r["committed"] = _i32(pool.max_seq_len + 64, dev)
         for name in ("tokens", "parents", "depth", "positions", "slots", "greedy"):
@@ -226,12 +227,16 @@ class FastRound:
                       "idx": torch.zeros(NB, nt, dtype=torch.int32, device=dev)}
         r["am_val"] = torch.zeros(NB, dtype=torch.float32, device=dev)
         r["taps"] = torch.zeros(NB, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
+        if remote is not None:
+            # the layer-epilogue copies write the tapped rows straight into the drafter GPU's buffer
+            assert remote.nodes == NB and remote.tap_width == len(tap_ids) * H
+            r["taps"] = remote.taps_on_drafter
         if head is not None:
             self._draft_buffers(r, head)
         # run every kernel once outside capture (module load, function attributes), then capture
         if self.tp is not None:
             self.tp.begin_sequence()
-        r["launches"] = self._launch_round(r, pdl=False)
+        r["launches"] = self._launch_round(r, pdl=False, use_remote=False)   # no handshakes while warming up
         torch.cuda.synchronize()
         X.status_word(dev).zero_()
         if self.tp is not None:
@@ -315,7 +320,7 @@ class FastRound:
                                 out_tok=d["topk_tok"], out_lp=d["topk_lp"])
         return n + 3
 
-    def _launch_round(self, r, pdl: bool) -> int:
+    def _launch_round(self, r, pdl: bool, use_remote: bool = True) -> int:
         lib, p, s = X.load(), X._p, X._stream
         pool, cfg = self.eng.pool, self.cfg
         NB, D, K = r["NB"], r["D"], r["K"]
@@ -326,6 +331,12 @@ class FastRound:
             if not r["staged"]:
                 r["topk_tok"].copy_(r["draft"]["topk_tok"][:D])
                 r["topk_lp"].copy_(r["draft"]["topk_lp"][:D])
+        remote = r.get("remote") if use_remote else None
+        if remote is not None and D > 0:
+            remote.target_wait_topk(pdl)
+            r["topk_tok"].copy_(remote.topk_on_target[0])
+            r["topk_lp"].copy_(remote.topk_on_target[1].view(torch.float32))
+            n += 1
         if r["staged"] and D > 0:
             r["topk_tok"].copy_(r["stage_tok"], non_blocking=True)
             r["topk_lp"].copy_(r["stage_lp"], non_blocking=True)
@@ -356,6 +367,9 @@ class FastRound:
                                            p(r["committed"]), r["committed"].numel(), p(r["eos"]), r["n_eos"],
                                            r["max_new"], p(r["path_idx"]), p(r["result"]), p(status), int(pdl), s()),
                  "js_tree_accept_commit")
+        if remote is not None:
+            remote.target_push_header(r["state"], r["committed"], r["path_idx"], pdl)
+            n += 4
         r["result_host"].copy_(r["result"], non_blocking=True)
         return n + 4
 
@@ -364,6 +378,9 @@ class FastRound:
         """Prefill through the eager kernel path and initialise the round's device state."""
         eng, pool = self.eng, self.eng.pool
         T = ids.shape[1]
+        remote = r.get("remote")
+        if remote is not None:
+            remote.reset()
         if self.tp is None:
             logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
             first = int(logits[-1].float().argmax())
@@ -393,6 +410,13 @@ class FastRound:
             state[ST_CTX] = n
         r["state"].copy_(state)
         torch.cuda.synchronize()
+        if remote is not None:
+            import torch.distributed as dist
+            hid = hidden.to(torch.bfloat16).contiguous()
+            dist.send(torch.tensor([hid.shape[0], hid.shape[1]], dtype=torch.int64, device=self.device),
+                      dst=remote.draft_rank, group=remote.group)
+            dist.send(hid, dst=remote.draft_rank, group=remote.group)
+            remote.target_push_raw_header(0, first, 0)
         if self.tp is not None:
             self.tp.begin_sequence()      # the graph's collectives restart their buffer cycle here
             self.tp.ring_mod = r.get("ring_mod", self.tp.ring_mod)
@@ -446,7 +470,13 @@ class FastRound:
         from .engine import bucket_for_n
         eng = self.eng
         D, K, NB = max(1, block_size - 1), int(tree_width), bucket_for_n(budget)
-        head, oracle, host_drafter = self._split_drafter(tree_drafter)
+        from .disagg import RemoteDraftHead
+        remote = None
+        if isinstance(tree_drafter, RemoteDraftHead):
+            remote, head, oracle, host_drafter = tree_drafter.channel, None, tree_drafter.oracle, None
+            taps = list(tree_drafter.target_layer_ids)
+        else:
+            head, oracle, host_drafter = self._split_drafter(tree_drafter)
         staged = oracle is not None or host_drafter is not None
         logit_free_caps = type(algo_obj).__name__ == "AccumLogP" or getattr(algo_obj, "force_baseline", False)
         if (host_drafter is not None and taps is not None) or (head is not None and not staged and not logit_free_caps):
@@ -459,8 +489,8 @@ class FastRound:
             taps = list(head.target_layer_ids) if taps is None else taps
             if head.block_size != block_size:
                 raise ValueError(f"draft head block_size {head.block_size} != block_size {block_size}")
-        r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens)
-        first = self._begin(r, sid, committed, taps if head is not None else None, total)
+        r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens, remote=remote)
+        first = self._begin(r, sid, committed, taps if (head is not None or remote is not None) else None, total)
         new_ids = [first]
         ctx_ids = committed[0].tolist() + [first]
         accept_lengths, tree_sizes, rounds = [], [], 0
@@ -510,6 +540,9 @@ class FastRound:
                     break
         if rounds:
             eng.pool.state(sid).length = int(res[4])
+        if remote is not None:
+            remote.target_push_raw_header(0, 0, 1)      # tell the drafter GPU this request is over
+            torch.cuda.synchronize()
         self.last_rounds = rounds
         self.last_device_ms = float(sum(a.elapsed_time(b) for a, b in events)) if events else 0.0
         new_ids = new_ids[: sp.max_new_tokens]

@@ -50,6 +50,24 @@ class SymmetricBuffer:
         self.ptrs_dev = torch.tensor(self.ptrs, dtype=torch.int64, device="cuda")
         dist.barrier(group=group)
 
+    def tensor(self, rank: int, shape, dtype, offset_bytes: int = 0) -> torch.Tensor:
+        """A tensor aliasing rank ``rank``'s buffer (peer memory when ``rank`` is not this rank).  Such a
+        tensor may be handed to THIS library's kernels as a destination or source; it must never be
+        given to a library kernel (GEMM, attention, NCCL) as an operand."""
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4", torch.int32: "<i4",
+                   torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+
+        class _Alias:
+            pass
+        a = _Alias()
+        a.__cuda_array_interface__ = {"shape": tuple(int(s) for s in shape), "typestr": typestr,
+                                      "data": (int(self.ptrs[rank]) + int(offset_bytes), False), "version": 3}
+        t = torch.as_tensor(a, device="cuda")
+        return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+    def zero_local(self) -> None:
+        self.tensor(self.rank, (self.nbytes,), torch.uint8).zero_()
+
     def close(self) -> None:
         for r, p in enumerate(self.ptrs):
             if r != self.rank and p:

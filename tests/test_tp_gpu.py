@@ -28,6 +28,11 @@ def test_tp_engine_two_ranks():
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
 
 
+def test_disaggregated_draft_head_two_ranks():
+    rc, out = _launch(2, "disagg")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp_engine_four_ranks():
     rc, out = _launch(4, "engine")

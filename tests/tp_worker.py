@@ -12,11 +12,55 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def disagg_main(rank):
+    """Target on rank 0, draft head on rank 1: the remote head must reproduce the local head's rounds."""
+    from jetspec_b200 import JetSpecEngine, SamplingParams, DraftHeadTreeDrafter
+    from jetspec_b200.engine.disagg import DraftWorker, RemoteDraftHead
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config, DraftHeadModel, draft_head_config
+    from jetspec_b200.parallel.handoff import HandoffChannel
+    cfg = Qwen3Config(vocab_size=8192, hidden_size=1024, intermediate_size=2048, num_hidden_layers=4,
+                      num_attention_heads=8, num_key_value_heads=8, head_dim=128)
+    model = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda", init="stable")
+    taps, D, K, budget = [0, 1, 3], 8, 4, 32
+    hcfg = draft_head_config(cfg, num_layers=1, block_size=D + 1, target_layer_ids=taps)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+    chan = HandoffChannel(None, nodes=32, tap_width=len(taps) * cfg.hidden_size, depth=D, width=K)
+    ok = True
+    if rank == 0:
+        prompt = torch.randint(0, cfg.vocab_size, (1, 40), generator=torch.Generator().manual_seed(0))
+        sp = SamplingParams(0.0, 40)
+        eng = JetSpecEngine(model, device="cuda:0", dtype=torch.bfloat16, max_seq_len=512)
+        local = eng.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=D + 1), tree_depth=D, tree_width=K,
+                                  budget=budget, sampling_params=sp, return_stats=True)
+        remote = eng.generate_tree(prompt, RemoteDraftHead(chan, taps, D + 1), tree_depth=D, tree_width=K,
+                                   budget=budget, sampling_params=sp, return_stats=True)
+        ok = (remote["token_ids"] == local["token_ids"] and remote["accept_lengths"] == local["accept_lengths"]
+              and remote["tree_sizes"] == local["tree_sizes"])
+        print(f"disaggregated drafting: tokens equal {remote['token_ids'] == local['token_ids']}, "
+              f"rounds {remote['rounds']} vs {local['rounds']}, same trees {remote['tree_sizes'] == local['tree_sizes']}", flush=True)
+    else:
+        worker = DraftWorker(head, model.model.embed_tokens.weight, model.lm_head.weight, chan, width=K,
+                             vocab_size=cfg.vocab_size, max_ctx=512)
+        steps = worker.serve()
+        print(f"draft worker served {steps} steps", flush=True)
+    from jetspec_b200.ops import cuda_ext as X
+    X.check_status("cuda")
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_WORKER_OK" if int(flag) == 1 else "TP_WORKER_FAILED", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 1 else 1)
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
+    if len(sys.argv) > 1 and sys.argv[1] == "disagg":
+        return disagg_main(rank)
     from jetspec_b200.ops import cuda_ext as X
     from jetspec_b200.parallel import TensorParallel, shard_cols, shard_rows
     X.load()
