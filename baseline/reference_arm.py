@@ -7,7 +7,9 @@ seeded weights our own arm uses) together with a minimal word-level tokenizer; p
 passed as token ids.  The engine is then built and driven exactly as the reference's own
 throughput script does (``bench/engine/tps_walltime.py:205-275``): backend
 ``triton_paged_tree_cudagraph_nogather``, fused GEMMs, ``GraphedDraftHead``, ``session=True``.
-The reference has no tensor parallelism: for N > 1 only rank 0 runs it, on one GPU.
+The reference's multi-GPU mode is data parallel (every rank a full replica with its own prompts,
+``bench/engine/tps_walltime.py:178-203``): for N > 1 every rank serves its own request from one
+shared scratch checkpoint and the line reports the sum of tokens over the slowest rank's time.
 
 If any step the reference needs cannot run on this box, the function prints
 ``{"impl": "reference", "unavailable": "<why>"}`` and returns.
@@ -91,106 +93,144 @@ def run_reference(args):
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dist.init_process_group("nccl")
+    scratch = os.path.join(tempfile.gettempdir(), f"jetspec_ref_{os.environ.get('MASTER_PORT', os.getpid())}")
     try:
-        if rank == 0:
-            _run(args, world)
+        res = _run(args, world, rank, scratch)
     except Exception as e:  # noqa: BLE001 - any failure of the reference stack is reported, not raised
         tb = traceback.format_exc().strip().splitlines()
-        _unavailable(f"{type(e).__name__}: {e} | {tb[-3] if len(tb) >= 3 else ''}")
+        res = {"unavailable": f"{type(e).__name__}: {e} | {tb[-3] if len(tb) >= 3 else ''}"}
+    try:
+        if world > 1:
+            import torch.distributed as dist
+            allres = [None] * world
+            dist.all_gather_object(allres, res)
+        else:
+            allres = [res]
+        if rank == 0:
+            _report(args, allres)
     finally:
         if world > 1:
             import torch.distributed as dist
             dist.barrier()
             dist.destroy_process_group()
+        if rank == 0:
+            shutil.rmtree(scratch, ignore_errors=True)
 
 
-def _run(args, world: int):
+def _sync_ranks(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def _run(args, world: int, rank: int, scratch: str) -> dict:
     if not os.path.isdir(os.path.join(REF, "jetspec")):
-        return _unavailable("reference package is not installed under baseline/_ref")
+        return {"unavailable": "reference package is not installed under baseline/_ref"}
     import torch
     if not torch.cuda.is_available():
-        return _unavailable("no CUDA device")
+        return {"unavailable": "no CUDA device"}
     sys.path.insert(0, REF)
     root = os.path.dirname(HERE)
     if root not in sys.path:
         sys.path.insert(1, root)
     os.environ.setdefault("JETSPEC_FUSE_GEMMS", "1")
-    cache = os.path.join(tempfile.gettempdir(), "jetspec_ref_cache")
+    cache = os.path.join(tempfile.gettempdir(), f"jetspec_ref_cache_{rank}")
     os.environ.setdefault("TORCHINDUCTOR_CACHE_DIR", os.path.join(cache, "inductor"))
     os.environ.setdefault("TRITON_CACHE_DIR", os.path.join(cache, "triton"))
-    from bench import ClockSampler, BASELINE_TOK_S
+    from bench import ClockSampler, model_config
     from jetspec_b200.drafters import OracleTreeDrafter, OracleOverrideDrafter
     dev = "cuda:0" if world == 1 else f"cuda:{os.environ.get('LOCAL_RANK', '0')}"
-    scratch = tempfile.mkdtemp(prefix="jetspec_ref_")
-    try:
-        cfg, tdir, hdir = build_checkpoints(args, scratch, dev)
-        from jetspec.inference_engine import JetSpecEngine, SamplingParams
-        from jetspec import load_draft_head
-        from jetspec.draft_head_adapter import GraphedDraftHead
-        eng = JetSpecEngine(tdir, device=dev, dtype=torch.bfloat16, block_size=16, attn_implementation="sdpa",
-                            attn_backend="triton_paged_tree_cudagraph_nogather", fuse_gemms=True)
-        head = load_draft_head(hdir, device=dev, dtype=torch.bfloat16, attn_implementation=eng.resolved_attn_implementation)
-        bs = args.tree_depth + 1
-        real = GraphedDraftHead(head, target=eng.model, block_size=bs, target_layer_ids=head.target_layer_ids,
-                                draft_shift=False)
-        prompt = torch.randint(0, cfg.vocab_size, (1, args.prompt_len),
-                               generator=torch.Generator().manual_seed(args.seed)).pin_memory()
-        sp = SamplingParams(0.0, args.max_new)
-        cont = prompt[0].tolist() + eng.generate(prompt, sp)["token_ids"]
-        max_accept = min(args.tree_depth, (args.budget - 2) // args.tree_width + 1)
-        oracle = OracleTreeDrafter(cont, cfg.vocab_size, tree_width=args.tree_width, mean_accept=args.mean_accept,
-                                   max_accept=max_accept, seed=args.seed)
-        drafter = OracleOverrideDrafter(real, oracle)
-        kw = dict(block_size=bs, tree_width=args.tree_width, budget=args.budget, tree_depth=args.tree_depth,
-                  algo="accum_logp", target_layer_ids=head.target_layer_ids, return_stats=True, sampling_params=sp,
-                  session=True, session_prompt_capacity=((args.prompt_len + 255) // 256) * 256)
-        converged = False
-        for it in range(6):
-            out = eng.generate_tree(prompt, drafter, **kw)
-            seq = prompt[0].tolist() + out["token_ids"]
-            if seq == oracle.sequence[:len(seq)]:
-                converged = True
-                break
-            oracle.set_continuation(seq)
-        for _ in range(args.warmup):
-            eng.generate_tree(prompt, drafter, **kw)
-        sampler = ClockSampler(torch.cuda.current_device())
-        torch.cuda.synchronize()
-        sampler.start()
-        toks, rounds, accept = 0, 0, []
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        e0.record()
-        for _ in range(args.steps):
-            out = eng.generate_tree(prompt, drafter, **kw)
-            toks += len(out["token_ids"])
-            rounds += out["rounds"]
-            accept += out["accept_lengths"]
-        e1.record()
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - t0
-        dev_ms = e0.elapsed_time(e1)
-        clocks = sampler.stop()
-        value = toks / (dev_ms / 1e3)
-        D, K = args.tree_depth, args.tree_width
-        print(json.dumps({
-            "metric": "decode tokens/s/request, Qwen3-8B tree budget 128", "value": round(value, 2),
-            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 4), "dtype": "bf16", "data": "synthetic",
-            "impl": "reference",
-            "config": {"model": f"{args.model} (random init, residual-dominant variant)", "global_batch": 1,
-                       "seq_len": args.prompt_len + args.max_new, "parallelism": "tp1 (the reference has no TP)",
-                       "backend": "triton_paged_tree_cudagraph_nogather + fuse_gemms + GraphedDraftHead + session",
-                       "tree": f"depth {D} width {K} budget {args.budget}",
-                       "mean_tokens_per_round": round(sum(accept) / max(1, len(accept)), 3),
-                       "ms_per_round": round(dev_ms / max(1, rounds), 4), "oracle_converged": converged,
-                       "timing": "CUDA events around whole requests (prefill included)",
-                       "l2": "inputs larger than L2 (16 GB of weights per round)"},
-            "clocks": clocks,
-            "e2e": {"value": round(toks / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": args.prompt_len * 8,
-                    "d2h_bytes_per_step": int(rounds / args.steps * 16)},
-            "gpu_launches": 0,
-        }), flush=True)
-    finally:
-        shutil.rmtree(scratch, ignore_errors=True)
+    err = None
+    if rank == 0:
+        try:
+            build_checkpoints(args, scratch, dev)
+        except Exception as e:  # noqa: BLE001
+            err = f"checkpoint export failed: {type(e).__name__}: {e}"
+    _sync_ranks(world)
+    if err or not os.path.isdir(os.path.join(scratch, "head")):
+        return {"unavailable": err or "checkpoint export failed on rank 0"}
+    cfg = model_config(args.model)
+    tdir, hdir = os.path.join(scratch, "target"), os.path.join(scratch, "head")
+    from jetspec.inference_engine import JetSpecEngine, SamplingParams
+    from jetspec import load_draft_head
+    from jetspec.draft_head_adapter import GraphedDraftHead
+    eng = JetSpecEngine(tdir, device=dev, dtype=torch.bfloat16, block_size=16, attn_implementation="sdpa",
+                        attn_backend="triton_paged_tree_cudagraph_nogather", fuse_gemms=True)
+    head = load_draft_head(hdir, device=dev, dtype=torch.bfloat16, attn_implementation=eng.resolved_attn_implementation)
+    bs = args.tree_depth + 1
+    real = GraphedDraftHead(head, target=eng.model, block_size=bs, target_layer_ids=head.target_layer_ids,
+                            draft_shift=False)
+    req_seed = args.seed + (rank if world > 1 else 0)
+    prompt = torch.randint(0, cfg.vocab_size, (1, args.prompt_len),
+                           generator=torch.Generator().manual_seed(req_seed)).pin_memory()
+    sp = SamplingParams(0.0, args.max_new)
+    cont = prompt[0].tolist() + eng.generate(prompt, sp)["token_ids"]
+    max_accept = min(args.tree_depth, (args.budget - 2) // args.tree_width + 1)
+    oracle = OracleTreeDrafter(cont, cfg.vocab_size, tree_width=args.tree_width, mean_accept=args.mean_accept,
+                               max_accept=max_accept, seed=req_seed)
+    drafter = OracleOverrideDrafter(real, oracle)
+    kw = dict(block_size=bs, tree_width=args.tree_width, budget=args.budget, tree_depth=args.tree_depth,
+              algo="accum_logp", target_layer_ids=head.target_layer_ids, return_stats=True, sampling_params=sp,
+              session=True, session_prompt_capacity=((args.prompt_len + 255) // 256) * 256)
+    converged = False
+    for it in range(6):
+        out = eng.generate_tree(prompt, drafter, **kw)
+        seq = prompt[0].tolist() + out["token_ids"]
+        if seq == oracle.sequence[:len(seq)]:
+            converged = True
+            break
+        oracle.set_continuation(seq)
+    for _ in range(args.warmup):
+        eng.generate_tree(prompt, drafter, **kw)
+    sampler = ClockSampler(torch.cuda.current_device())
+    torch.cuda.synchronize()
+    _sync_ranks(world)
+    sampler.start()
+    toks, rounds, accept = 0, 0, []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        out = eng.generate_tree(prompt, drafter, **kw)
+        toks += len(out["token_ids"])
+        rounds += out["rounds"]
+        accept += out["accept_lengths"]
+    e1.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    return {"toks": toks, "rounds": rounds, "acc_sum": float(sum(accept)), "acc_n": len(accept), "wall": wall,
+            "dev_ms": e0.elapsed_time(e1), "clocks": sampler.stop(), "converged": converged}
+
+
+def _report(args, allres: list) -> None:
+    from bench import BASELINE_TOK_S
+    bad = [r for r in allres if "unavailable" in r]
+    if bad:
+        return _unavailable(bad[0]["unavailable"])
+    n = len(allres)
+    toks, rounds = sum(r["toks"] for r in allres), sum(r["rounds"] for r in allres)
+    dev_ms, wall = max(r["dev_ms"] for r in allres), max(r["wall"] for r in allres)
+    acc = sum(r["acc_sum"] for r in allres) / max(1, sum(r["acc_n"] for r in allres))
+    value = toks / (dev_ms / 1e3)
+    D, K = args.tree_depth, args.tree_width
+    print(json.dumps({
+        "metric": "decode tokens/s/request, Qwen3-8B tree budget 128", "value": round(value, 2),
+        "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / BASELINE_TOK_S, 4), "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": {"model": f"{args.model} (random init, residual-dominant variant)", "global_batch": n,
+                   "seq_len": args.prompt_len + args.max_new, "parallelism": f"dp{n}",
+                   "tokens_per_s_per_request": round(value / n, 2),
+                   "backend": "triton_paged_tree_cudagraph_nogather + fuse_gemms + GraphedDraftHead + session",
+                   "tree": f"depth {D} width {K} budget {args.budget}",
+                   "mean_tokens_per_round": round(acc, 3),
+                   "ms_per_round": round(dev_ms * n / max(1, rounds), 4),
+                   "oracle_converged": all(r["converged"] for r in allres),
+                   "timing": "CUDA events around whole requests (prefill included), max over ranks",
+                   "l2": "inputs larger than L2 (16 GB of weights per round)"},
+        "clocks": allres[0]["clocks"],
+        "e2e": {"value": round(toks / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": n * args.prompt_len * 8,
+                "d2h_bytes_per_step": int(rounds / args.steps * 16)},
+        "gpu_launches": 0,
+    }), flush=True)
