@@ -112,7 +112,8 @@ _status: dict = {}
 
 def status_word(device) -> torch.Tensor:
     """Per-device int32 the kernels write an error code to (0 = ok)."""
-    key = torch.device(device).index or 0
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else (torch.cuda.current_device() if dev.type == "cuda" else -1)
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]

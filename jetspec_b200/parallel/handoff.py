@@ -62,10 +62,12 @@ class HandoffChannel:
         b = torch.zeros(8, dtype=torch.int32, device="cuda")
         f = torch.ones(1, dtype=torch.int32, device="cuda")
         e = torch.zeros(1, dtype=torch.int32, device="cuda")
+        e2 = torch.zeros(1, dtype=torch.int32, device="cuda")     # kept alive until the kernels have run
+        status = X.status_word("cuda")
         s = X._stream()
         lib.js_push_words(X._p(a), X._p(b), 8, 0, s)
         lib.js_flag_push(X._p(b), X._p(e), 0, s)
-        lib.js_flag_wait(X._p(f), X._p(torch.zeros(1, dtype=torch.int32, device="cuda")), X._p(X.status_word("cuda")), 0, s)
+        lib.js_flag_wait(X._p(f), X._p(e2), X._p(status), 0, s)
         lib.js_make_header(X._p(a), X._p(b), X._p(a[4:]), 0, s)
         lib.js_draft_apply_header(X._p(a), X._p(b), X._p(a[4:]), 0, s)
         torch.cuda.synchronize()
