@@ -79,6 +79,14 @@ JS_DEVICE void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, 
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, bytes a multiple of 16).
+JS_DEVICE void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 JS_DEVICE void tmem_alloc(uint32_t* smem_result, uint32_t cols) {  // whole warp, cols = power of two >= 32
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
@@ -133,6 +141,36 @@ JS_DEVICE uint64_t umma_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
 JS_DEVICE constexpr uint32_t umma_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// ---- NVFP4 (block-scaled e2m1) -------------------------------------------------------------
+// Shared-memory descriptor of one 512-byte scale tile (32 rows of 16 bytes, unswizzled; groups of
+// 8 rows are 128 bytes apart).
+JS_DEVICE uint64_t umma_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;              // stride byte offset = 128 B
+  d |= static_cast<uint64_t>(1) << 46;                     // descriptor version (Blackwell)
+  return d;
+}
+// Copy 32 rows x 16 bytes from shared memory into 4 tensor-memory columns, replicated to the four
+// 32-lane groups (the placement block-scaled MMAs read their scale factors from).  One thread issues.
+JS_DEVICE void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Instruction descriptor: e2m1 x e2m1 with e4m3 scales per 16 elements -> fp32, K-major operands.
+JS_DEVICE constexpr uint32_t umma_idesc_nvfp4(int M, int N) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+// D[tmem] (+)= (A * SFA) * (B * SFB), K = 64 per instruction; sfa / sfb are tensor-memory addresses.
+JS_DEVICE void umma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
 }
 
 // ---------------------------------------------------------------- clusters

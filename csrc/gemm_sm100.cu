@@ -15,7 +15,14 @@
 // CTA accumulates its K range, parks the partial tile in its own shared memory, and after a
 // cluster barrier every CTA reduces and finishes a column slice of the tile by reading its
 // peers' partials through distributed shared memory — no global round trip, no atomics,
-// deterministic summation order.
+// deterministic summation order.  (Partials are PUSHED: each CTA stores its chunks into the
+// owning peer's receive area with st.shared::cluster, so the reduce reads local memory only.)
+//
+// NVFP4 mode (template flag FP4): both operands are packed e2m1 (256 elements per 128-byte
+// swizzle row, so one stage carries four K=64 MMAs), the e4m3 block scales arrive with plain
+// bulk copies in 512-byte tiles (128 rows x 4 blocks), are copied to tensor memory with
+// tcgen05.cp and consumed by tcgen05.mma.kind::mxf4nvf4.block_scale; the epilogue applies the
+// per-row activation scale times the per-tensor weight scale.
 //
 // Epilogues: plain store (+ residual), SwiGLU (the tile holds BN/2 gate and BN/2 up columns
 // of the same outputs), per-tile argmax partials (LM head), per-tile top-8 + log-sum-exp
@@ -58,6 +65,11 @@ struct GemmParams {
   const float* row_weight;
   __nv_bfloat16* const* peer_pairs;
   int* const* peer_cnt;
+  // NVFP4 mode: block scales of A and W in 512-byte tiles, per-row scale of A, per-tensor scale of W
+  const uint8_t* sfa;
+  const uint8_t* sfw;
+  const float* row_scale;
+  float w_scale;
 };
 
 JS_DEVICE void red_release_sys_add(int* addr, int v) {
@@ -83,13 +95,15 @@ JS_DEVICE unsigned long long gtime() {
 // BUDGET_KB bounds the pipeline's shared memory: ~96 KB lets two CTAs share an SM (more tiles
 // in flight, natural load balance when the tile count is not a multiple of 148), ~192 KB gives
 // one CTA per SM a deeper pipeline.
-template <int BN, int BUDGET_KB>
+template <int BN, int BUDGET_KB, bool FP4 = false>
 struct GemmSmem {
-  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageA = BM * BK * 2;      // 128-byte rows in both modes
   static constexpr int kStageW = BN * BK * 2;
-  static constexpr int kStage = kStageA + kStageW;
+  static constexpr int kStageSF = FP4 ? 2048 + (BN / 128) * 2048 : 0;   // 4 scale tiles of A + 4 per 128 rows of W
+  static constexpr int kStage = kStageA + kStageW + kStageSF;
   static constexpr int kBudget = BUDGET_KB * 1024;
-  static constexpr int kStages = (kBudget / kStage) > 8 ? 8 : ((kBudget / kStage) < 2 ? 2 : (kBudget / kStage));
+  static constexpr int kMaxStages = FP4 ? 4 : 8;   // FP4: every stage also owns 32 tensor-memory columns of scales
+  static constexpr int kStages = (kBudget / kStage) > kMaxStages ? kMaxStages : ((kBudget / kStage) < 2 ? 2 : (kBudget / kStage));
   static constexpr int kMinBlocks = BUDGET_KB <= 100 ? 2 : 1;
   static constexpr int kTiles = kStages * kStage;
 };
@@ -105,12 +119,16 @@ __host__ __device__ inline int recv_bytes(int split, int bn, bool swiglu) {
   return split > 1 ? split * recv_slots_per_src(split, bn, swiglu) * 16384 : 0;
 }
 
-template <int BN, int EPI, int BUDGET_KB>
-__global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB>::kMinBlocks)
+template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
+__global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB, FP4>::kMinBlocks)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, GemmParams p) {
-  using S = GemmSmem<BN, BUDGET_KB>;
+  using S = GemmSmem<BN, BUDGET_KB, FP4>;
   constexpr int kStages = S::kStages;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;   // power of two for BN in {32,64,128,256}
+  static_assert(!FP4 || BN == 128, "the NVFP4 path is built for 128-column tiles");
+  // FP4: accumulator in columns [0,128), block scales of stage s in [128 + 32 s, 128 + 32 s + 32)
+  constexpr uint32_t kTmemCols = FP4 ? 256 : (BN < 32 ? 32 : BN);   // power of two
+  constexpr int kXStep = FP4 ? 128 : BK;              // TMA x advance per k-block (bytes resp. bf16 elements)
+  constexpr int kKPerBlock = FP4 ? 256 : BK;          // K elements per pipeline stage
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,7 +151,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int m_end = grouped ? p.group_off[expert + 1] : p.M;
   const int wn0 = expert * p.N + n0;         // row of this tile in the (stacked) weight matrix
   if (m0 >= m_end) return;                   // this expert has fewer row tiles (uniform for the CTA)
-  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_total = (p.K + kKPerBlock - 1) / kKPerBlock;
   const int kb_begin = (kb_total * z) / split;
   const int kb_end = (kb_total * (z + 1)) / split;
   const int nkb = kb_end - kb_begin;
@@ -167,25 +185,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       JS_TRACE(1);   // setup done, first TMA about to issue
       // Weights do not depend on the previous kernel: start streaming them before waiting on it.
       const int pre = nkb < kStages ? nkb : kStages;
+      // FP4: scale tiles of k-block kb are 4 consecutive 512-byte tiles of this operand's row tile
+      const size_t sf_row = static_cast<size_t>(p.K / 64) * 512;
+      auto load_sfw = [&](int s, int kb) {
+        if constexpr (FP4)
+          bulk_load_1d(smem + s * S::kStage + S::kStageA + S::kStageW + 2048,
+                       p.sfw + static_cast<size_t>(wn0 / 128) * sf_row + static_cast<size_t>(kb) * 2048, 2048, &full_bar[s]);
+      };
+      auto load_sfa = [&](int s, int kb) {
+        if constexpr (FP4)
+          bulk_load_1d(smem + s * S::kStage + S::kStageA + S::kStageW,
+                       p.sfa + static_cast<size_t>(m0 / 128) * sf_row + static_cast<size_t>(kb) * 2048, 2048, &full_bar[s]);
+      };
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], S::kStage);
-        tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * BK, wn0);
+        tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * kXStep, wn0);
+        load_sfw(i, kb_begin + i);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * S::kStage, &tmA, &full_bar[i], (kb_begin + i) * BK, m0);
+      for (int i = 0; i < pre; ++i) {
+        tma_load_2d(smem + i * S::kStage, &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0);
+        load_sfa(i, kb_begin + i);
+      }
       for (int i = pre; i < nkb; ++i) {
         const int s = i % kStages;
         const uint32_t ph = (i / kStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) break;
         mbar_expect_tx(&full_bar[s], S::kStage);
-        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * BK, wn0);
-        tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * BK, m0);
+        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * kXStep, wn0);
+        tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * kXStep, m0);
+        load_sfw(s, kb_begin + i);
+        load_sfa(s, kb_begin + i);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = FP4 ? umma_idesc_nvfp4(BM, BN) : umma_idesc_bf16(BM, BN);
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % kStages;
@@ -196,10 +231,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage));
         const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage + S::kStageA));
+        if constexpr (FP4) {
+          // scale tiles: shared memory -> tensor memory (4 columns per 128 rows x 4 blocks), then
+          // four K=64 MMAs, each reading its own 4+4 scale columns
+          const uint32_t sf_smem = smem_u32(smem + s * S::kStage + S::kStageA + S::kStageW);
+          const uint32_t sf_tmem = tmem_base + 128 + s * 32;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing K by 16 elements = 32 bytes inside the swizzle row = +2 in 16-byte units
-          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            tmem_cp_32x128b_warpx4(sf_tmem + 4 * k, umma_desc_sf(sf_smem + 512 * k));
+            tmem_cp_32x128b_warpx4(sf_tmem + 16 + 4 * k, umma_desc_sf(sf_smem + 2048 + 512 * k));
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // advancing K by 64 e2m1 = 32 bytes inside the swizzle row = +2 in 16-byte units
+            umma_nvfp4(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_tmem + 4 * k, sf_tmem + 16 + 4 * k,
+                       (i | k) != 0 ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 elements = 32 bytes inside the swizzle row = +2 in 16-byte units
+            umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
       }
@@ -272,6 +325,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += base[j * BM];
         }
+      }
+      if constexpr (FP4) {
+        const float alpha = grow < m_end ? p.row_scale[grow] * p.w_scale : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= alpha;
       }
     };
 
@@ -549,12 +607,26 @@ static int make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t col
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int BN, int EPI, int BUDGET_KB>
+// 2-D packed-e2m1 matrix seen as bytes: [rows, row_bytes] with leading dimension ld_bytes, box = [box_rows, 128 bytes]
+static int make_map_u8(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t row_bytes, uint64_t ld_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {ld_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
                        cudaStream_t stream, int groups = 0, int group_m_tiles = 0) {
-  using S = GemmSmem<BN, BUDGET_KB>;
+  using S = GemmSmem<BN, BUDGET_KB, FP4>;
   static int configured = 0;
-  auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB>;
+  auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4>;
   const int smem_bytes = S::kTiles + recv_bytes(split, BN, EPI == EPI_SWIGLU) + 1024 /*align slack*/ + 256 /*barriers*/;
   if (smem_bytes > 227 * 1024) return -18;
   if (smem_bytes > configured) {
@@ -676,4 +748,66 @@ extern "C" int js_gemm_bf16_grouped(const void* A, const void* W, void* C, int t
     return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
   }
   return -17;
+}
+
+// NVFP4 GEMM: C[M,N] = (Aq * sfa * row_scale) * (Wq * sfw * w_scale)^T.  Aq (M, K/2) and Wq (N, K/2) hold two
+// e2m1 codes per byte; sfa / sfw are the e4m3 block scales in 512-byte tiles of 128 rows x 4 blocks, row tiles
+// outermost (sfa must cover ceil(M/128)*128 rows, sfw ceil(N/128)*128); row_scale has M floats.
+// epi: 0 store(+residual), 1 swiglu, 4 fp32 store.  K % 256 == 0.
+extern "C" int js_gemm_nvfp4(const void* Aq, const void* sfa, const float* row_scale, const void* Wq, const void* sfw,
+                             float w_scale, void* C, const void* residual, int M, int N, int K, int lda_bytes,
+                             int ldw_bytes, int ldc, int epi, int split, int* status, int pdl, cudaStream_t stream) {
+  using namespace js;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 256) || (lda_bytes % 16) || (ldw_bytes % 16)) return -10;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Wq) | reinterpret_cast<uintptr_t>(sfa) |
+       reinterpret_cast<uintptr_t>(sfw)) & 15) return -11;
+  if (split < 1 || split > 4 || split > K / 256) return -12;
+  if (epi == EPI_SWIGLU && split > 2) return -14;
+  if ((epi == EPI_STORE || epi == EPI_SWIGLU) && (ldc % 8)) return -15;
+  if (!row_scale) return -22;
+  CUtensorMap ta, tw;
+  if (make_map_u8(&ta, Aq, M, K / 2, lda_bytes, BM) || make_map_u8(&tw, Wq, N, K / 2, ldw_bytes, 128)) return -16;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.status = status; p.world = 1;
+  p.sfa = reinterpret_cast<const uint8_t*>(sfa); p.sfw = reinterpret_cast<const uint8_t*>(sfw);
+  p.row_scale = row_scale; p.w_scale = w_scale;
+#define JS_CASE4(EPI_)                                                                                   \
+  if (epi == EPI_)                                                                                        \
+    return split > 1 ? launch_gemm<128, EPI_, 128, true>(ta, tw, p, split, pdl != 0, stream)              \
+                     : launch_gemm<128, EPI_, 160, true>(ta, tw, p, split, pdl != 0, stream);
+  JS_CASE4(EPI_STORE) JS_CASE4(EPI_SWIGLU) JS_CASE4(EPI_STORE_F32)
+#undef JS_CASE4
+  return -17;
+}
+
+// Row-parallel NVFP4 GEMM fused with the tensor-parallel all-reduce (same protocol as js_gemm_bf16_allreduce).
+extern "C" int js_gemm_nvfp4_allreduce(const void* Aq, const void* sfa, const float* row_scale, const void* Wq,
+                                       const void* sfw, float w_scale, void* C, const void* residual, int M, int N,
+                                       int K, int lda_bytes, int ldw_bytes, int ldc, int split, void* const* peer_recv,
+                                       int* const* peer_flags, int rank, int world, int m_cap, int n_flags, int* status,
+                                       int pdl, cudaStream_t stream) {
+  using namespace js;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K % 256) || (lda_bytes % 16) || (ldw_bytes % 16) || (ldc % 8) || (N % 8)) return -10;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Wq) | reinterpret_cast<uintptr_t>(sfa) |
+       reinterpret_cast<uintptr_t>(sfw)) & 15) return -11;
+  if (split < 1 || split > 4 || split > K / 256) return -12;
+  if (M > m_cap || world < 1 || rank < 0 || rank >= world || !row_scale) return -19;
+  const int ctas = ((N + 127) / 128) * ((M + BM - 1) / BM) * split;
+  if (ctas > n_flags) return -20;
+  if (ctas > 148) return -21;           // every CTA must be resident: CTAs wait for peers on other GPUs
+  CUtensorMap ta, tw;
+  if (make_map_u8(&ta, Aq, M, K / 2, lda_bytes, BM) || make_map_u8(&tw, Wq, N, K / 2, ldw_bytes, 128)) return -16;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.status = status;
+  p.peer_recv = reinterpret_cast<__nv_bfloat16* const*>(peer_recv); p.peer_flags = peer_flags;
+  p.rank = rank; p.world = world; p.m_cap = m_cap;
+  p.sfa = reinterpret_cast<const uint8_t*>(sfa); p.sfw = reinterpret_cast<const uint8_t*>(sfw);
+  p.row_scale = row_scale; p.w_scale = w_scale;
+  return launch_gemm<128, EPI_ALLREDUCE, 128, true>(ta, tw, p, split, pdl != 0, stream);
 }

@@ -46,7 +46,11 @@ def _e2m1_decode(code: torch.Tensor) -> torch.Tensor:
 
 @dataclass
 class NVFP4Tensor:
-    """A quantised matrix; ``outer`` is a 0-d tensor (per tensor) or ``(rows,)`` (per row)."""
+    """A quantised matrix; ``outer`` is a 0-d tensor (per tensor) or ``(rows,)`` (per row).
+
+    Rows are independent given the outer scale, so row slices, row concatenations (of tensors that share
+    one outer scale) and row permutations are exact; K can be cut at multiples of 64.
+    """
     packed: torch.Tensor
     scales: torch.Tensor
     outer: torch.Tensor
@@ -57,11 +61,51 @@ class NVFP4Tensor:
     def device(self):
         return self.packed.device
 
+    @property
+    def dtype(self):
+        return torch.uint8
+
     def dequantize(self, dtype=torch.float32) -> torch.Tensor:
         return dequantize_nvfp4(self, dtype)
 
     def nbytes(self) -> int:
         return self.packed.numel() + self.scales.numel() + 4 * max(1, self.outer.numel())
+
+    def swizzled(self) -> "NVFP4Tensor":
+        """Make sure the tile-ordered copy of the block scales exists (the tensor-core kernel reads it)."""
+        if self.scales_swizzled is None:
+            self.scales_swizzled = swizzle_scales(self.scales)
+        return self
+
+    def to(self, device) -> "NVFP4Tensor":
+        sw = self.scales_swizzled.to(device) if self.scales_swizzled is not None else None
+        return NVFP4Tensor(self.packed.to(device), self.scales.to(device), self.outer.to(device), self.shape, sw)
+
+    def _outer_rows(self, sel):
+        return self.outer[sel] if self.outer.dim() == 1 else self.outer
+
+    def rows(self, a: int, b: int) -> "NVFP4Tensor":
+        return NVFP4Tensor(self.packed[a:b], self.scales[a:b], self._outer_rows(slice(a, b)), (b - a, self.shape[1]))
+
+    def index_rows(self, idx: torch.Tensor) -> "NVFP4Tensor":
+        return NVFP4Tensor(self.packed[idx].contiguous(), self.scales.view(torch.uint8)[idx].contiguous()
+                           .view(torch.float8_e4m3fn), self._outer_rows(idx), (int(idx.numel()), self.shape[1]))
+
+    def cols(self, k0: int, k1: int) -> "NVFP4Tensor":
+        if k0 % 64 or k1 % 64:
+            raise ValueError("NVFP4 matrices can be cut along K at multiples of 64 only")
+        return NVFP4Tensor(self.packed[:, k0 // 2:k1 // 2].contiguous(),
+                           self.scales.view(torch.uint8)[:, k0 // BLOCK:k1 // BLOCK].contiguous().view(torch.float8_e4m3fn),
+                           self.outer, (self.shape[0], k1 - k0))
+
+    @staticmethod
+    def cat_rows(parts: list) -> "NVFP4Tensor":
+        o = parts[0].outer
+        if o.dim() != 0 or any(p.outer.dim() != 0 or float(p.outer) != float(o) for p in parts):
+            raise ValueError("only matrices that share one per-tensor scale can be stacked")
+        return NVFP4Tensor(torch.cat([p.packed for p in parts], 0).contiguous(),
+                           torch.cat([p.scales.view(torch.uint8) for p in parts], 0).contiguous().view(torch.float8_e4m3fn),
+                           o, (sum(p.shape[0] for p in parts), parts[0].shape[1]))
 
 
 def quantize_nvfp4(x: torch.Tensor, per_row: bool = False, swizzle: bool = True) -> NVFP4Tensor:
@@ -72,10 +116,14 @@ def quantize_nvfp4(x: torch.Tensor, per_row: bool = False, swizzle: bool = True)
     rows, K = x.shape
     xf = x.detach().float()
     amax = xf.abs().amax(dim=1) if per_row else xf.abs().amax()
-    outer = (amax / (E2M1_MAX * E4M3_MAX)).clamp_min(1e-30)
+    # divisors are device tensors: dividing a CUDA tensor by a Python number multiplies by the rounded
+    # reciprocal instead, which would make the bytes depend on the device
+    c_full = torch.tensor(E2M1_MAX * E4M3_MAX, dtype=torch.float32, device=xf.device)
+    c_six = torch.tensor(E2M1_MAX, dtype=torch.float32, device=xf.device)
+    outer = torch.div(amax, c_full).clamp_min(1e-30)
     blocks = xf.view(rows, K // BLOCK, BLOCK)
     o = outer.view(-1, 1) if per_row else outer
-    want = blocks.abs().amax(dim=2) / E2M1_MAX / o                        # block scale before rounding
+    want = torch.div(torch.div(blocks.abs().amax(dim=2), c_six), o)       # block scale before rounding
     scales = want.clamp(max=E4M3_MAX).to(torch.float8_e4m3fn)
     sf = scales.float() * o                                                # the scale the decoder will apply
     q = torch.where(sf.unsqueeze(-1) > 0, blocks / sf.unsqueeze(-1).clamp_min(1e-30), torch.zeros_like(blocks))
@@ -121,38 +169,51 @@ def nvfp4_linear_reference(x: torch.Tensor, w: NVFP4Tensor, quantize_input: bool
     xf = x.float()
     if quantize_input:
         xf = quantize_nvfp4(xf, per_row=True, swizzle=False).dequantize()
-    return xf @ w.dequantize().t()
+    wd = w.__dict__.get("_deq")
+    if wd is None:                      # the oracle keeps the dequantised weight (CPU tests call it every step)
+        wd = w.dequantize()
+        w.__dict__["_deq"] = wd
+    return xf @ wd.t()
 
 
 class NVFP4Linear(torch.nn.Module):
-    """Drop-in for ``nn.Linear(bias=False)`` holding NVFP4 weights; activations are quantised per call.
+    """Stand-in for ``nn.Linear(bias=False)`` holding NVFP4 weights; activations are quantised per call
+    (one outer scale per row).  ``.weight`` is the :class:`NVFP4Tensor`, which ``ops.linear`` understands, so
+    model code written as ``ops.linear(x, proj.weight, proj.bias)`` runs unchanged.
 
     On a CUDA device the product runs on the block-scaled tensor-core kernel; elsewhere on the oracle.
     """
+    bias = None
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight):
         super().__init__()
-        q = quantize_nvfp4(weight, per_row=False)
+        q = weight if isinstance(weight, NVFP4Tensor) else quantize_nvfp4(weight, per_row=False)
         self.out_features, self.in_features = q.shape
-        self.register_buffer("packed", q.packed)
-        self.register_buffer("scales", q.scales.view(torch.uint8))
-        self.register_buffer("scales_swizzled", q.scales_swizzled)
-        self.register_buffer("outer", q.outer)
+        self.register_buffer("packed", q.packed.contiguous())
+        self.register_buffer("scales", q.scales.contiguous().view(torch.uint8))
+        self.register_buffer("outer", q.outer.clone())
 
     @property
-    def qweight(self) -> NVFP4Tensor:
-        return NVFP4Tensor(self.packed, self.scales.view(torch.float8_e4m3fn), self.outer,
-                           (self.out_features, self.in_features), self.scales_swizzled)
+    def weight(self) -> NVFP4Tensor:
+        q = self.__dict__.get("_q")
+        if q is None or q.packed.data_ptr() != self.packed.data_ptr():     # rebuilt after .to(device)
+            q = NVFP4Tensor(self.packed, self.scales.view(torch.float8_e4m3fn), self.outer,
+                            (self.out_features, self.in_features))
+            self.__dict__["_q"] = q
+        return q
+
+    qweight = weight
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
         shp = x.shape
-        x2 = x.reshape(-1, shp[-1])
-        if x2.is_cuda and x2.dtype == torch.bfloat16:
-            from ..ops import cuda_ext as X
-            y = X.gemm_nvfp4(x2.contiguous(), self.qweight)
-        else:
-            y = nvfp4_linear_reference(x2, self.qweight).to(x.dtype)
+        y = ops.linear(x.reshape(-1, shp[-1]), self.weight)
         return y.view(*shp[:-1], self.out_features)
+
+
+# projections that read the same activations are quantised as ONE matrix, so that the fused
+# (QKV, gate|up) weights the kernels use are row stacks of exactly the per-projection weights
+_GROUPS = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))
 
 
 def quantize_model_nvfp4(model: torch.nn.Module, skip=("lm_head", "embed_tokens")) -> int:
@@ -160,10 +221,26 @@ def quantize_model_nvfp4(model: torch.nn.Module, skip=("lm_head", "embed_tokens"
     Returns the number of layers converted."""
     n = 0
     for name, mod in list(model.named_modules()):
-        for cname, child in list(mod.named_children()):
+        kids = dict(mod.named_children())
+
+        def ok(cname):
+            c = kids.get(cname)
             full = f"{name}.{cname}" if name else cname
-            if isinstance(child, torch.nn.Linear) and child.bias is None and not any(s in full for s in skip) \
-                    and child.in_features % 64 == 0:
-                setattr(mod, cname, NVFP4Linear(child.weight.data))
+            return (isinstance(c, torch.nn.Linear) and c.bias is None and c.in_features % 64 == 0
+                    and not any(s in full for s in skip))
+        done = set()
+        for group in _GROUPS:
+            if all(ok(c) for c in group):
+                q = quantize_nvfp4(torch.cat([kids[c].weight.data for c in group], 0), swizzle=False)
+                r0 = 0
+                for c in group:
+                    r1 = r0 + kids[c].out_features
+                    setattr(mod, c, NVFP4Linear(q.rows(r0, r1)))
+                    r0 = r1
+                    done.add(c)
+                    n += 1
+        for cname in kids:
+            if cname not in done and ok(cname):
+                setattr(mod, cname, NVFP4Linear(kids[cname].weight.data))
                 n += 1
     return n

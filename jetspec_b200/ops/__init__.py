@@ -36,6 +36,11 @@ def add_rmsnorm(residual, x, weight, eps: float = 1e-6):
 
 
 def linear(x, w, bias: Optional[torch.Tensor] = None):
+    if not isinstance(w, torch.Tensor):            # an NVFP4Tensor: 4-bit weights, activations quantised per row
+        from ..models.nvfp4 import nvfp4_linear_reference
+        if _kern(x) and x.dim() == 2 and w.shape[1] % 256 == 0:
+            return _ext().gemm_nvfp4(x.contiguous(), w.swizzled())
+        return nvfp4_linear_reference(x, w).to(x.dtype)
     if _kern(x) and bias is None and x.dim() == 2 and w.dtype == torch.bfloat16:
         from . import cuda_ext
         if cuda_ext.gemm_supported(x.shape[0], w.shape[0], x.shape[1]):

@@ -231,6 +231,71 @@ def n_tiles(N: int, bn: int = 128) -> int:
     return (N + bn - 1) // bn
 
 
+# ------------------------------------------------------------------ NVFP4
+def nvfp4_act_buffers(M: int, K: int, device) -> dict:
+    """Device buffers one quantised activation matrix needs (allocate once, reuse across graph replays)."""
+    tiles = (M + 127) // 128
+    return {"packed": torch.zeros(M, K // 2, dtype=torch.uint8, device=device),
+            "sf": torch.zeros(tiles * (K // 64) * 512, dtype=torch.uint8, device=device),
+            "outer": torch.zeros(M, dtype=torch.float32, device=device), "M": M, "K": K}
+
+
+def quant_nvfp4(x: torch.Tensor, buf: Optional[dict] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                norm_out: Optional[torch.Tensor] = None, pdl: bool = False) -> dict:
+    """Quantise ``x (M, K)`` bf16 to NVFP4 with one outer scale per row; with ``norm_w`` the RMSNorm of ``x`` is
+    quantised instead (and also written to ``norm_out`` as bf16 when given)."""
+    lib = load()
+    M, K = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if buf is None:
+        buf = nvfp4_act_buffers(M, K, x.device)
+    assert buf["K"] == K and buf["M"] >= M
+    lib.js_quant_nvfp4.restype = ctypes.c_int
+    rc = lib.js_quant_nvfp4(_p(x), x.stride(0), _p(norm_w), ctypes.c_float(eps), M, K, _p(buf["packed"]), _p(buf["sf"]),
+                            _p(buf["outer"]), _p(norm_out), norm_out.stride(0) if norm_out is not None else 0,
+                            int(pdl), _stream())
+    _check(rc, f"js_quant_nvfp4(M={M},K={K})")
+    return buf
+
+
+def pick_nvfp4_split(M: int, N: int, K: int, epi: int) -> int:
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    kb = K // 256
+    max_split = 2 if epi == EPI_SWIGLU else 4
+    split = 1
+    while split < max_split and tiles * (split + 1) <= SM_COUNT and kb // (split + 1) >= 2:
+        split += 1
+    return split
+
+
+def gemm_nvfp4(x, qw, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+               epi: int = EPI_STORE, split: Optional[int] = None, pdl: bool = False, act_buf: Optional[dict] = None):
+    """``out = q(x) @ dequant(qw).T`` on the block-scaled tcgen05 kernel.
+
+    ``x`` is either a bf16 ``(M, K)`` matrix (quantised here, per row) or the dict ``quant_nvfp4`` returned;
+    ``qw`` is an ``NVFP4Tensor`` with per-tensor outer scale and swizzled block scales.
+    """
+    lib = load()
+    act = x if isinstance(x, dict) else quant_nvfp4(x, act_buf, pdl=pdl)
+    M = x.shape[0] if not isinstance(x, dict) else act.get("rows", act["M"])
+    N, K = qw.shape
+    assert act["K"] == K
+    qw.swizzled()
+    split = split or pick_nvfp4_split(M, N, K, epi)
+    dev = qw.packed.device
+    if out is None:
+        out = torch.empty(M, N // 2 if epi == EPI_SWIGLU else N,
+                          dtype=torch.float32 if epi == EPI_STORE_F32 else torch.bfloat16, device=dev)
+    if not hasattr(qw, "_w_scale"):
+        qw._w_scale = float(qw.outer)           # one host read per weight, outside any graph capture
+    lib.js_gemm_nvfp4.restype = ctypes.c_int
+    rc = lib.js_gemm_nvfp4(_p(act["packed"]), _p(act["sf"]), _p(act["outer"]), _p(qw.packed), _p(qw.scales_swizzled),
+                           ctypes.c_float(qw._w_scale), _p(out), _p(residual), M, N, K, act["packed"].stride(0),
+                           qw.packed.stride(0), out.stride(0), epi, split, _p(status_word(dev)), int(pdl), _stream())
+    _check(rc, f"js_gemm_nvfp4(M={M},N={N},K={K},epi={epi},split={split})")
+    return out
+
+
 def lm_head_argmax(h: torch.Tensor, w: torch.Tensor, ws: Optional[dict] = None, pdl: bool = False,
                    out_idx: Optional[torch.Tensor] = None, out_val: Optional[torch.Tensor] = None):
     """Greedy token per row: vocabulary GEMM with a per-tile argmax epilogue, then a merge.
