@@ -24,6 +24,7 @@ from ..core.llm import decode_text
 from ..drafters.head import DraftHeadTreeDrafter
 from ..drafters.oracle import OracleOverrideDrafter, OracleTreeDrafter
 from ..models.qwen3 import MLP
+from ..parallel.tp import stack_rows
 from ..ops import cuda_ext as X
 from ..ops import reference as ref
 from ..sampling import SamplingParams, sample
@@ -61,7 +62,7 @@ def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
             m = shard_mlp(layer.mlp, tp.rank, tp.world, lambda g, u: X.interleave_gate_up(g, u, 128))
             d.update({"gu": m["gu"], "down": m["down"]})
             out.append(d)
-        return out
+        return _finish_layer_weights(out)
     for layer in layers:
         if not isinstance(layer.mlp, MLP):
             raise NotImplementedError("the graph path covers dense MLP layers")
@@ -70,12 +71,24 @@ def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
             raise NotImplementedError("the graph path covers bias-free attention projections")
         out.append({
             "ln1": layer.input_layernorm.weight, "ln2": layer.post_attention_layernorm.weight,
-            "qkv": torch.cat((a.q_proj.weight, a.k_proj.weight, a.v_proj.weight), 0).contiguous(),
-            "kv": torch.cat((a.k_proj.weight, a.v_proj.weight), 0).contiguous(),
+            "qkv": stack_rows([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight]),
+            "kv": stack_rows([a.k_proj.weight, a.v_proj.weight]),
             "qn": a.q_norm.weight, "kn": a.k_norm.weight, "o": a.o_proj.weight,
             "gu": X.interleave_gate_up(layer.mlp.gate_proj.weight, layer.mlp.up_proj.weight, 128),
             "down": layer.mlp.down_proj.weight,
         })
+    return _finish_layer_weights(out)
+
+
+def _finish_layer_weights(out: list) -> list:
+    """NVFP4 layers: build the tile-ordered block scales and read the per-tensor scales once, up front."""
+    for d in out:
+        d["fp4"] = not isinstance(d["qkv"], torch.Tensor)
+        if d["fp4"]:
+            for k in ("qkv", "kv", "o", "gu", "down"):
+                if k in d:
+                    d[k].swizzled()
+                    d[k]._w_scale = float(d[k].outer)
     return out
 
 
@@ -93,12 +106,42 @@ class _Stack:
         self.q = torch.zeros(T, Hq, D, **bf)
         self.attn = torch.zeros(T, Hq * D, **bf)
         self.act = torch.zeros(T, I, **bf)
+        self._q4: dict = {}
         npt = max(1, 64 // (Hq // Hkv))
         self.splits = X.attn_splits((T + npt - 1) // npt, Hkv, max_keys)
         self.attn_ws = None
         if self.splits > 1:
             self.attn_ws = {"o": torch.zeros(self.splits, T, Hq, D, dtype=torch.float32, device=device),
                             "ml": torch.zeros(self.splits, T, Hq, 2, dtype=torch.float32, device=device)}
+
+
+def _q4(st: _Stack, K: int) -> dict:
+    """The stack's NVFP4 staging buffers for activations of width ``K`` (allocated on first use)."""
+    if K not in st._q4:
+        st._q4[K] = X.nvfp4_act_buffers(st.T, K, st.x.device)
+    return st._q4[K]
+
+
+def _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) -> int:
+    """One decoder layer on NVFP4 weights: every GEMM input is quantised on the fly (the two norms are fused
+    into their quantisation kernels) and multiplied on the block-scaled tensor-core path."""
+    eps = cfg.rms_norm_eps
+    h4 = X.quant_nvfp4(st.x, _q4(st, st.x.shape[1]), norm_w=L["ln1"], eps=eps, pdl=pdl)
+    X.gemm_nvfp4(h4, L["qkv"], out=st.qkv, pdl=pdl)
+    attend()
+    a4 = X.quant_nvfp4(st.attn, _q4(st, st.attn.shape[1]), pdl=pdl)
+    if tp is None:
+        X.gemm_nvfp4(a4, L["o"], out=st.x, residual=st.x, pdl=pdl)
+    else:
+        tp.gemm_allreduce_nvfp4(a4, L["o"], st.x, residual=st.x, pdl=pdl)
+    h4 = X.quant_nvfp4(st.x, _q4(st, st.x.shape[1]), norm_w=L["ln2"], eps=eps, pdl=pdl)
+    X.gemm_nvfp4(h4, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
+    m4 = X.quant_nvfp4(st.act, _q4(st, st.act.shape[1]), pdl=pdl)
+    if tp is None:
+        X.gemm_nvfp4(m4, L["down"], out=st.x, residual=st.x, pdl=pdl)
+    else:
+        tp.gemm_allreduce_nvfp4(m4, L["down"], st.x, residual=st.x, pdl=pdl)
+    return 8
 
 
 def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
@@ -109,11 +152,22 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
     last = len(layers) - 1
     n = 0
     for li, L in enumerate(layers):
+        def attend(li=li, L=L):
+            X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps,
+                       pdl=pdl)
+            X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits,
+                                   scale, causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
+        if L.get("fp4"):
+            n += _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) + 2 + (1 if st.splits > 1 else 0)
+            if taps is not None and li != last:
+                for j, t in enumerate(tap_ids):
+                    if t == li:
+                        X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
+                        n += 1
+            continue
         X.rmsnorm(st.x, L["ln1"], eps, out=st.h, pdl=pdl)
         X.gemm(st.h, L["qkv"], out=st.qkv, pdl=pdl)
-        X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps, pdl=pdl)
-        X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits, scale,
-                               causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
+        attend()
         if tp is None:
             X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
         else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory

@@ -222,6 +222,10 @@ def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor, bn: int = 128) 
     I, H = gate_w.shape
     h = bn // 2
     assert I % h == 0
+    if not isinstance(gate_w, torch.Tensor):      # NVFP4: stack, then permute rows (exact: rows are independent)
+        t = torch.arange(I, device=gate_w.packed.device).view(I // h, h)
+        order = torch.cat((t, t + I), dim=1).reshape(-1)
+        return type(gate_w).cat_rows([gate_w, up_w]).index_rows(order)
     g = gate_w.view(I // h, h, H)
     u = up_w.view(I // h, h, H)
     return torch.cat((g, u), dim=1).reshape(2 * I, H).contiguous()

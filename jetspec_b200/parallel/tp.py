@@ -29,18 +29,29 @@ from .symm import SymmetricBuffer
 
 
 # --------------------------------------------------------------------------- sharding math (device-free)
-def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
-    """Column-parallel: split the OUTPUT features (rows of an ``nn.Linear`` weight)."""
+def shard_rows(w, rank: int, world: int):
+    """Column-parallel: split the OUTPUT features (rows of an ``nn.Linear`` weight, bf16 or NVFP4)."""
     n = w.shape[0]
     assert n % world == 0, f"{n} output features do not divide over {world} ranks"
+    if not isinstance(w, torch.Tensor):
+        return w.rows(rank * (n // world), (rank + 1) * (n // world))
     return w[rank * (n // world):(rank + 1) * (n // world)].contiguous()
 
 
-def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
-    """Row-parallel: split the INPUT features (columns of an ``nn.Linear`` weight)."""
+def shard_cols(w, rank: int, world: int):
+    """Row-parallel: split the INPUT features (columns of an ``nn.Linear`` weight, bf16 or NVFP4)."""
     k = w.shape[1]
     assert k % world == 0, f"{k} input features do not divide over {world} ranks"
+    if not isinstance(w, torch.Tensor):
+        return w.cols(rank * (k // world), (rank + 1) * (k // world))
     return w[:, rank * (k // world):(rank + 1) * (k // world)].contiguous()
+
+
+def stack_rows(parts: list):
+    """Row stack of weights that are all bf16 matrices or all NVFP4 matrices sharing one outer scale."""
+    if not isinstance(parts[0], torch.Tensor):
+        return type(parts[0]).cat_rows(list(parts))
+    return torch.cat(tuple(parts), 0).contiguous()
 
 
 def shard_attention(layer, cfg, rank: int, world: int) -> dict:
@@ -48,7 +59,7 @@ def shard_attention(layer, cfg, rank: int, world: int) -> dict:
     a = layer.self_attn
     assert cfg.num_attention_heads % world == 0 and cfg.num_key_value_heads % world == 0
     q, k, v = (shard_rows(t.weight, rank, world) for t in (a.q_proj, a.k_proj, a.v_proj))
-    return {"qkv": torch.cat((q, k, v), 0).contiguous(), "o": shard_cols(a.o_proj.weight, rank, world),
+    return {"qkv": stack_rows([q, k, v]), "o": shard_cols(a.o_proj.weight, rank, world),
             "qn": a.q_norm.weight, "kn": a.k_norm.weight}
 
 
@@ -118,6 +129,36 @@ class TensorParallel:
                                         self.rank, self.world, self.m_cap, self.n_flags,
                                         X._p(X.status_word(x.device)), int(pdl), X._stream())
         X._check(rc, f"js_gemm_bf16_allreduce(M={M},N={N},K={K},split={split})")
+        self.launches += 1
+        return out
+
+    def gemm_allreduce_nvfp4(self, act: dict, qw, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                             split: Optional[int] = None, pdl: bool = False):
+        """NVFP4 twin of :meth:`gemm_allreduce`: ``act`` is this rank's quantised K-slice of the activations
+        (``cuda_ext.quant_nvfp4``), ``qw`` this rank's K-slice of the 4-bit weight."""
+        X = self._X
+        lib = X.load()
+        M = act.get("rows", act["M"])
+        N, K = qw.shape
+        assert N <= self.n_max and M <= self.m_cap and act["K"] == K
+        qw.swizzled()
+        if not hasattr(qw, "_w_scale"):
+            qw._w_scale = float(qw.outer)
+        if split is None:
+            tiles = ((N + 127) // 128) * ((M + 127) // 128)
+            split = 1
+            while split < 4 and tiles * (split + 1) <= X.SM_COUNT and (K // 256) // (split + 1) >= 1:
+                split += 1
+        t = self._turn % self.ring_mod
+        self._turn += 1
+        lib.js_gemm_nvfp4_allreduce.restype = ctypes.c_int
+        rc = lib.js_gemm_nvfp4_allreduce(X._p(act["packed"]), X._p(act["sf"]), X._p(act["outer"]), X._p(qw.packed),
+                                         X._p(qw.scales_swizzled), ctypes.c_float(qw._w_scale), X._p(out),
+                                         X._p(residual), M, N, K, act["packed"].stride(0), qw.packed.stride(0),
+                                         out.stride(0), split, X._p(self.recv[t].ptrs_dev),
+                                         X._p(self.flags[t].ptrs_dev), self.rank, self.world, self.m_cap,
+                                         self.n_flags, X._p(X.status_word(out.device)), int(pdl), X._stream())
+        X._check(rc, f"js_gemm_nvfp4_allreduce(M={M},N={N},K={K},split={split})")
         self.launches += 1
         return out
 

@@ -164,3 +164,27 @@ def test_nvfp4_linear_module_on_gpu(ext):
     y = lin(x)
     ref = nvfp4_linear_reference(x.view(-1, 1024), lin.qweight).view(3, 9, 512)
     assert y.shape == (3, 9, 512) and float((y.float() - ref).abs().max() / ref.abs().max()) < 8e-3
+
+
+@pytest.mark.gpu
+def test_engine_on_nvfp4_weights_is_lossless_and_tracks_the_oracle(ext):
+    """Graph-captured AR and tree rounds on 4-bit weights: the tree path reproduces the AR tokens, and both follow
+    the fp32 oracle that multiplies the same codes and scales with plain PyTorch."""
+    import copy
+    from jetspec_b200 import JetSpecEngine, LLM, SamplingParams, RandomTreeDrafter
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    cfg = Qwen3Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128)
+    model = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda", init="stable")
+    assert quantize_model_nvfp4(model) == 7 * cfg.num_hidden_layers
+    prompt = torch.randint(0, 4096, (1, 48), generator=torch.Generator().manual_seed(0))
+    sp = SamplingParams(0.0, 40)
+    eng = JetSpecEngine(model, device="cuda", dtype=torch.bfloat16, max_seq_len=1024)
+    ar = eng.generate(prompt, sp)["token_ids"]
+    tree = eng.generate_tree(prompt, RandomTreeDrafter(4096, seed=1), tree_depth=8, tree_width=4, budget=60,
+                             sampling_params=sp, return_stats=True)
+    assert tree["token_ids"] == ar
+    oracle = LLM(copy.deepcopy(model).float(), device="cuda", dtype=torch.float32).generate(prompt, sp)["token_ids"]
+    agree = sum(a == b for a, b in zip(ar, oracle)) / len(ar)
+    assert agree > 0.9
+    ext.check_status("cuda")
