@@ -104,9 +104,11 @@ def main():
         print(f"tp argmax: worst shortfall {gap:.3e}", flush=True)
     ok &= gap < 0.05
     ok &= ep_check(rank, world)
+    ok &= nvfp4_check(tp, rank, world)
     X.check_status("cuda")
     if len(sys.argv) > 1 and sys.argv[1] == "engine":
         ok &= engine_check(tp, rank, world)
+        ok &= engine_check(tp, rank, world, nvfp4=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -144,12 +146,48 @@ def ep_check(rank, world) -> bool:
     return err < 2e-2 and same
 
 
-def engine_check(tp, rank, world) -> bool:
+def nvfp4_check(tp, rank, world) -> bool:
+    """Row-parallel NVFP4 GEMM fused with the all-reduce against the dequantised per-rank products."""
+    from jetspec_b200.ops import cuda_ext as X
+    from jetspec_b200.models.nvfp4 import quantize_nvfp4, nvfp4_linear_reference
+    from jetspec_b200.parallel import shard_cols
+    g = torch.Generator(device="cuda").manual_seed(11)
+    good = True
+    for (M, N, K) in [(128, 4096, 4096), (21, 1024, 2048), (1, 4096, 12288 // 2 * 2)]:
+        if (K // world) % 256:
+            continue
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g, device="cuda") * 0.03).to(torch.bfloat16)
+        res = torch.randn(M, N, generator=g, device="cuda").to(torch.bfloat16)
+        qw = quantize_nvfp4(w.float(), swizzle=False)
+        ql = shard_cols(qw, rank, world)
+        xl = shard_cols(x, rank, world)
+        for rep_ in range(5):
+            out = res.clone()
+            tp.gemm_allreduce_nvfp4(X.quant_nvfp4(xl), ql, out, residual=out)
+            torch.cuda.synchronize()
+        part = nvfp4_linear_reference(xl, ql)
+        dist.all_reduce(part)
+        ref = part + res.float()
+        err = float((out.float() - ref).abs().max() / ref.abs().max())
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        if rank == 0:
+            print(f"nvfp4 gemm_allreduce M={M} N={N} K={K}: rel err {err:.2e}, replicas identical {same}", flush=True)
+        good &= err < 1.5e-2 and same
+    return good
+
+
+def engine_check(tp, rank, world, nvfp4: bool = False) -> bool:
     from jetspec_b200 import JetSpecEngine, SamplingParams, OracleTreeDrafter
     from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
     cfg = Qwen3Config(vocab_size=8192, hidden_size=1024, intermediate_size=2048, num_hidden_layers=4,
                       num_attention_heads=8, num_key_value_heads=8, head_dim=128)
     model = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda", init="stable")
+    if nvfp4:
+        from jetspec_b200.models.nvfp4 import quantize_model_nvfp4
+        quantize_model_nvfp4(model)
     prompt = torch.randint(0, cfg.vocab_size, (1, 40), generator=torch.Generator().manual_seed(0))
     sp = SamplingParams(0.0, 48)
     eng = JetSpecEngine(model, device=f"cuda:{torch.cuda.current_device()}", dtype=torch.bfloat16, max_seq_len=512,
@@ -160,7 +198,7 @@ def engine_check(tp, rank, world) -> bool:
     out = eng.generate_tree(prompt, oracle, tree_depth=8, tree_width=4, budget=32, sampling_params=sp, return_stats=True)
     good = ar == expect and out["token_ids"] == expect and out["tpf"] > 2.0
     if rank == 0:
-        print(f"tp engine: AR ok {ar == expect}, tree ok {out['token_ids'] == expect}, tokens/round {out['tpf']:.2f}", flush=True)
+        print(f"tp engine{' (nvfp4)' if nvfp4 else ''}: AR ok {ar == expect}, tree ok {out['token_ids'] == expect}, tokens/round {out['tpf']:.2f}", flush=True)
     return good
 
 
