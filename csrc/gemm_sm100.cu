@@ -119,6 +119,11 @@ __host__ __device__ inline int recv_bytes(int split, int bn, bool swiglu) {
   return split > 1 ? split * recv_slots_per_src(split, bn, swiglu) * 16384 : 0;
 }
 
+// The receive area shares the stages' memory only when the two do not fit side by side.
+__host__ __device__ inline bool recv_aliases_stages(int tiles_bytes, int recv_total) {
+  return recv_total > 0 && tiles_bytes + recv_total + 1280 > 227 * 1024;
+}
+
 template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
 __global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB, FP4>::kMinBlocks)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, GemmParams p) {
@@ -132,10 +137,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // [pipeline stages][split-K receive area][barriers]; the receive area is separate from the
-  // stages because peers push into it while this CTA may still be streaming
+  // [pipeline stages][split-K receive area][barriers].  Peers push into the receive area while
+  // this CTA may still be streaming, so it normally sits behind the stages; only when both do
+  // not fit (deep pipeline) it ALIASES them, guarded by one more cluster barrier after the main loop.
   const bool grouped = p.group_off != nullptr;
-  const int data_bytes = S::kTiles + recv_bytes(grouped ? 1 : gridDim.z, BN, EPI == EPI_SWIGLU);
+  const int recv_total = recv_bytes(grouped ? 1 : gridDim.z, BN, EPI == EPI_SWIGLU);
+  const bool alias = recv_aliases_stages(S::kTiles, recv_total);
+  const int data_bytes = alias ? (S::kTiles > recv_total ? S::kTiles : recv_total) : S::kTiles + recv_total;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + data_bytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* accum_bar = empty_bar + kStages;
@@ -271,7 +279,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int kHC = (kSwiglu ? BN / 2 : BN) / 32;          // owned-chunk index space
   const int per_owner = (kHC + split - 1) / split;
   const int slots_per_src = kSwiglu ? 2 * per_owner : per_owner;
-  const uint32_t recv_addr = smem_u32(smem + S::kTiles);
+  const uint32_t recv_addr = smem_u32(smem + (alias ? 0 : S::kTiles));
   // TMEM chunk `ch` (32 columns) is finished by CTA owner_of(ch); local_of(ch) is its slot there
   auto owner_of = [&](int ch) { return (ch % kHC) % split; };
   auto local_of = [&](int ch) { return (ch % kHC) / split + (ch >= kHC ? per_owner : 0); };
@@ -285,6 +293,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   if (split > 1) {
+    if (alias) {   // every CTA of the cluster has finished its main loop (its stages are dead) before anyone pushes
+      tc_fence_before();
+      __syncthreads();
+      cluster_sync();
+    }
     // push every chunk of the partial tile into its owner's receive area (remote stores are
     // fire-and-forget; the cluster barrier below makes them visible)
     if (epi_warp && acc_ok) {
@@ -307,7 +320,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   if (epi_warp && acc_ok) {
-    const float* recv = reinterpret_cast<const float*>(smem + S::kTiles);
+    const float* recv = reinterpret_cast<const float*>(smem + (alias ? 0 : S::kTiles));
     // fetch 32 consecutive accumulator columns of this thread's row, reduced over the K split
     auto load_chunk = [&](int c0, float* v) {
       if (split == 1) {
@@ -627,7 +640,10 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   using S = GemmSmem<BN, BUDGET_KB, FP4>;
   static int configured = 0;
   auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4>;
-  const int smem_bytes = S::kTiles + recv_bytes(split, BN, EPI == EPI_SWIGLU) + 1024 /*align slack*/ + 256 /*barriers*/;
+  const int recv_total = recv_bytes(split, BN, EPI == EPI_SWIGLU);
+  const int data_bytes = recv_aliases_stages(S::kTiles, recv_total) ? (S::kTiles > recv_total ? S::kTiles : recv_total)
+                                                                     : S::kTiles + recv_total;
+  const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/;
   if (smem_bytes > 227 * 1024) return -18;
   if (smem_bytes > configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;
@@ -659,8 +675,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
 }  // namespace js
 
 // C = A[M,K] * W[N,K]^T.  epi: 0 store(+residual) 1 swiglu 2 argmax partials 3 top-8 + lse partials 4 fp32 store.
-// bn in {32,64,128,256}; split = K-split cluster size (1..4; store/swiglu only); deep != 0 selects the
-// one-CTA-per-SM deep pipeline instead of the two-CTAs-per-SM one.  Returns 0 or a negative code.
+// bn in {64,128,256}; split = K-split cluster size (1..4; store/swiglu only); deep selects the pipeline's
+// shared-memory budget: 0 = 96 KB (two CTAs per SM), 2 = 128 KB, 1 = 192 KB (one CTA per SM).
+// Returns 0 or a negative code.
 extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* residual, int M, int N, int K, int lda,
                             int ldw, int ldc, int epi, int bn, int split, int deep, float* part_val, int* part_idx,
                             float* part_lse, int* status, unsigned long long* trace, int pdl,
@@ -681,9 +698,9 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
                nullptr, nullptr, 0, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr};
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
-    return (split > 1 && BN_ < 256) ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
-           : (deep && split == 1)   ? launch_gemm<BN_, EPI_, 192>(ta, tw, p, split, pdl != 0, stream)   \
-                                    : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
+    return deep == 2 ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
+           : deep == 1 ? launch_gemm<BN_, EPI_, 192>(ta, tw, p, split, pdl != 0, stream)   \
+                       : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
   JS_CASE(64, EPI_STORE) JS_CASE(128, EPI_STORE) JS_CASE(256, EPI_STORE)
   JS_CASE(128, EPI_STORE_F32)
   JS_CASE(128, EPI_SWIGLU) JS_CASE(256, EPI_SWIGLU)

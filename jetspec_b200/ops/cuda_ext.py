@@ -173,19 +173,20 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int):
     tiles = m_tiles * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
     split = 1
-    deep = _DEEP
     if epi in (EPI_STORE, EPI_STORE_F32, EPI_SWIGLU):
         max_split = 4 if epi != EPI_SWIGLU else 2
-        # first choice: one CTA per SM with the deep pipeline (fewest CTAs that still cover the chip)
-        one = 1
-        while one < max_split and tiles * (one + 1) <= SM_COUNT and kb // (one + 1) >= 4:
-            one += 1
-        if tiles * one >= SM_COUNT * 3 // 4 and tiles * one <= SM_COUNT:
-            return bn, one, True
-        slots = 2 * SM_COUNT
-        while split < max_split and tiles * (split + 1) <= slots and kb // (split + 1) >= 4:
-            split += 1
-    return bn, split, deep
+        # Measured on chains of L2-cold GEMMs (M = 128): a K split helps while the whole grid is one
+        # wave of one CTA per SM AND the clusters can be placed (a cluster lives inside one GPC, so only
+        # ~32 clusters of 4, ~40 of 3 or ~72 of 2 fit at once; 48 clusters of 3 ran as two waves).
+        room = {2: 72, 3: 40, 4: 32}
+        for c in (4, 3, 2):
+            if c <= max_split and tiles <= room[c] and tiles * c <= SM_COUNT and kb // c >= 4:
+                split = c
+                break
+    if split > 1:
+        return bn, split, 1            # deep pipeline; the receive area aliases the stages
+    # no split: a deep pipeline when the tiles fit one CTA per SM, else two shallow CTAs per SM
+    return bn, 1, (1 if tiles <= SM_COUNT or _DEEP else 0)
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -210,7 +211,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     ldc = out.stride(0) if out is not None else 0
     rc = lib.js_gemm_bf16(_p(x), _p(w), _p(out), _p(residual), M, N, K, x.stride(0), w.stride(0), ldc, epi, bn,
-                          split, int(bool(deep)), _p(part_val), _p(part_idx), _p(part_lse),
+                          split, int(deep), _p(part_val), _p(part_idx), _p(part_lse),
                           _p(status_word(x.device)), _p(trace), int(pdl), _stream())
     _check(rc, f"js_gemm_bf16(M={M},N={N},K={K},epi={epi},bn={bn},split={split})")
     return out
