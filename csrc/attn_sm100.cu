@@ -381,3 +381,21 @@ extern "C" int js_paged_tree_attention(const void* q, const void* k_pool, const 
     default: return -14;
   }
 }
+
+// Merge the key splits of a (splits, T, Hq, 128) fp32 workspace with its (max, sum) pairs into out (T, Hq*128).
+extern "C" int js_attn_merge(float* ws_o, float* ws_ml, void* out, int T, int Hq, int splits, int pdl, cudaStream_t stream) {
+  using namespace js;
+  AttnParams p{};
+  p.ws_o = ws_o; p.ws_ml = ws_ml; p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.T = T; p.Hq = Hq; p.splits = splits;
+  cudaLaunchConfig_t c2 = {};
+  c2.gridDim = dim3((T * Hq + 7) / 8);
+  c2.blockDim = dim3(256);
+  c2.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  c2.attrs = attr;
+  c2.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c2, attn_merge_kernel, p) == cudaSuccess ? 0 : -5;
+}

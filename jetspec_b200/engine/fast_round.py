@@ -107,8 +107,7 @@ class _Stack:
         self.attn = torch.zeros(T, Hq * D, **bf)
         self.act = torch.zeros(T, I, **bf)
         self._q4: dict = {}
-        npt = max(1, 64 // (Hq // Hkv))
-        self.splits = X.attn_splits((T + npt - 1) // npt, Hkv, max_keys)
+        self.splits = X.attn_splits_for(T, Hq, Hkv, max_keys)
         self.attn_ws = None
         if self.splits > 1:
             self.attn_ws = {"o": torch.zeros(self.splits, T, Hq, D, dtype=torch.float32, device=device),

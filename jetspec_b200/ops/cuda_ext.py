@@ -409,9 +409,29 @@ def attn_splits(q_tiles: int, Hkv: int, max_keys: int) -> int:
     return max(1, min(want, (max_keys + 127) // 128, 16))
 
 
+ATTN_IMPL = os.environ.get("JETSPEC_ATTN", "tc")     # "tc": tcgen05 kernel where it applies; "mma": mma.sync kernel
+
+
+def attn_impl(Hq: int, Hkv: int, W: int = 0) -> str:
+    G = Hq // Hkv
+    return "tc" if ATTN_IMPL == "tc" and 128 % G == 0 and W <= 8 else "mma"
+
+
+def attn_splits_for(T: int, Hq: int, Hkv: int, max_keys: int) -> int:
+    """Key splits for ``T`` query tokens: fill the SMs with ONE wave of CTAs, a couple of key tiles per split."""
+    G = Hq // Hkv
+    if attn_impl(Hq, Hkv) == "tc":                      # 128 rows per CTA, one CTA per SM
+        npt = 128 // G
+        ctas = max(1, ((T + npt - 1) // npt) * Hkv)
+        return max(1, min(SM_COUNT // ctas, (max_keys + 127) // 128, 16))
+    npt = max(1, 64 // G)
+    return attn_splits((T + npt - 1) // npt, Hkv, max_keys)
+
+
 def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens, mask_bits, scale: float,
                          causal: bool, max_q: int, out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
-                         ws: Optional[dict] = None, max_keys: Optional[int] = None, pdl: bool = False):
+                         ws: Optional[dict] = None, max_keys: Optional[int] = None, pdl: bool = False,
+                         impl: Optional[str] = None):
     """Ragged paged attention with tree (packed-bit) or causal masking.  See
     :func:`jetspec_b200.ops.reference.paged_tree_attention` for the contract."""
     lib = load()
@@ -423,9 +443,8 @@ def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
     if out is None:
         out = torch.empty(T, Hq * D, dtype=q.dtype, device=q.device)
     if splits is None:
-        npt = max(1, 64 // G)
         mk = max_keys if max_keys is not None else slot_map.shape[1]
-        splits = attn_splits((T + npt - 1) // npt, Hkv, mk)
+        splits = attn_splits_for(T, Hq, Hkv, mk)
     ws_o = ws_ml = None
     if splits > 1:
         if ws is None:
@@ -433,11 +452,14 @@ def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
                   "ml": torch.empty(splits, T, Hq, 2, dtype=torch.float32, device=q.device)}
         ws_o, ws_ml = ws["o"], ws["ml"]
     W = mask_bits.shape[1] if mask_bits is not None else 0
-    _check(lib.js_paged_tree_attention(_p(q), _p(k_pool), _p(v_pool), _p(slot_map), _p(seq_rows), _p(cu_q),
-                                       _p(past_lens), _p(mask_bits), _p(out), _p(ws_o), _p(ws_ml),
-                                       _p(status_word(q.device)), B, T, Hq, Hkv, S, slot_map.shape[1], W,
-                                       int(bool(causal)), int(splits), ctypes.c_float(scale), int(pdl), _stream()),
-           "js_paged_tree_attention")
+    impl = impl or attn_impl(Hq, Hkv, W)
+    fn = lib.js_paged_tree_attention_tc if impl == "tc" else lib.js_paged_tree_attention
+    fn.restype = ctypes.c_int
+    _check(fn(_p(q), _p(k_pool), _p(v_pool), _p(slot_map), _p(seq_rows), _p(cu_q),
+              _p(past_lens), _p(mask_bits), _p(out), _p(ws_o), _p(ws_ml),
+              _p(status_word(q.device)), B, T, Hq, Hkv, S, slot_map.shape[1], W,
+              int(bool(causal)), int(splits), ctypes.c_float(scale), int(pdl), _stream()),
+           f"js_paged_tree_attention[{impl}]")
     return out
 
 

@@ -138,7 +138,8 @@ def _random_tree_bits(n, words, rng):
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (8, 1), (4, 4)])
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("causal", [False, True])
-def test_paged_tree_attention(ext, Hq, Hkv, splits, causal):
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_paged_tree_attention(ext, Hq, Hkv, splits, causal, impl):
     from jetspec_b200.ops import reference as ref
     rng = random.Random(7)
     D, S, max_len = 128, 4096, 1024
@@ -167,7 +168,8 @@ def test_paged_tree_attention(ext, Hq, Hkv, splits, causal):
     seq_rows = torch.tensor(rows, dtype=torch.int32, device="cuda")
     past = torch.tensor(pasts, dtype=torch.int32, device="cuda")
     scale = 1 / math.sqrt(D)
-    out = ext.paged_tree_attention(q, kp, vp, slot_map, seq_rows, cu, past, bits, scale, causal, max(ns), splits=splits)
+    out = ext.paged_tree_attention(q, kp, vp, slot_map, seq_rows, cu, past, bits, scale, causal, max(ns), splits=splits,
+                                   impl=impl)
     exp = ref.paged_tree_attention(q.float(), kp.float(), vp.float(), slot_map, seq_rows, cu, past, bits, scale, causal)
     torch.cuda.synchronize()
     assert rel_err(out, exp) < BF16_TOL
