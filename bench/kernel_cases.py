@@ -3,6 +3,7 @@
     python bench/kernel_cases.py gemm        # the four decoder GEMM shapes of Qwen3-8B at 128 rows
     python bench/kernel_cases.py attention   # paged tree attention, 128 nodes over a 1.5k-token prefix
     python bench/kernel_cases.py lm_head     # vocabulary GEMM with the argmax epilogue
+    python bench/kernel_cases.py nvfp4       # activation quantiser + block-scaled GEMM on the same four shapes
 
 Each case holds well under a few GB on the device and launches its kernel a handful of times, so a
 profiler capture of it ends by itself.
@@ -35,6 +36,23 @@ def case_gemm(reps: int = 2):
     torch.cuda.synchronize()
 
 
+def case_nvfp4(reps: int = 2):
+    from jetspec_b200.models.nvfp4 import quantize_nvfp4
+    M, H, I = 128, 4096, 12288
+    x, a = bf(M, H), bf(M, I)
+    w = {k: quantize_nvfp4(v.float()) for k, v in
+         {"qkv": bf(6144, H, scale=0.02), "o": bf(H, H, scale=0.02), "gu": bf(2 * I, H, scale=0.02),
+          "down": bf(H, I, scale=0.02)}.items()}
+    res = bf(M, H)
+    for _ in range(reps):
+        xq, aq = X.quant_nvfp4(x), X.quant_nvfp4(a)
+        X.gemm_nvfp4(xq, w["qkv"])
+        X.gemm_nvfp4(xq, w["o"], out=res, residual=res)
+        X.gemm_nvfp4(xq, w["gu"], epi=X.EPI_SWIGLU)
+        X.gemm_nvfp4(aq, w["down"], out=res, residual=res)
+    torch.cuda.synchronize()
+
+
 def case_lm_head(reps: int = 2):
     h, w = bf(128, 4096), bf(151936, 4096, scale=0.02)
     for _ in range(reps):
@@ -60,6 +78,6 @@ def case_attention(reps: int = 2):
 
 if __name__ == "__main__":
     X.load()
-    {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention}[sys.argv[1]]()
+    {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4}[sys.argv[1]]()
     X.check_status("cuda")
     print("ok")

@@ -14,8 +14,8 @@
 //   * warp 4 issues all MMAs: QK(t+1) is issued before PV(t), so the tensor pipe works on the next
 //     scores while the softmax of the current tile runs.
 //
-// Roles (288 threads): warps 0-3 softmax + epilogue (tensor-memory lane quadrant = warp id),
-// warp 4 MMA issuer / TMEM owner, warps 5-8 loaders.  Every wait is bounded (status word).
+// Roles (416 threads): warps 0-3 softmax + epilogue (tensor-memory lane quadrant = warp id),
+// warp 4 MMA issuer / TMEM owner, warps 5-12 loaders.  Every wait is bounded (status word).
 #include "common.cuh"
 
 #include <math.h>
@@ -26,7 +26,8 @@ constexpr int TD = 128;          // head dim
 constexpr int TROWS = 128;       // query rows per CTA
 constexpr int TKEYS = 64;        // keys per tile
 constexpr int TSTAGES = 3;
-constexpr int TTHREADS = 288;
+constexpr int TLOADERS = 256;       // loader threads (gather throughput grows with the copies in flight)
+constexpr int TTHREADS = 160 + TLOADERS;
 constexpr int kStageKV = 2 * TKEYS * 256;      // K then V, each 2 halves x 64 keys x 128 B
 constexpr int kSmemQ = TROWS * 256;            // 2 halves x 128 rows x 128 B
 constexpr int kSmemP = TROWS * 128;            // 128 rows x 64 keys bf16
@@ -47,6 +48,7 @@ struct AttnTcParams {
   int* status;
   int B, T, Hq, Hkv, S, max_len, W, causal, splits;
   float scale_log2;
+  int cluster_merge;           // the key splits of a tile form a cluster and merge through distributed shared memory
 };
 
 JS_DEVICE void cp_async16_tc(uint32_t smem_addr, const void* gmem, bool valid) {
@@ -68,6 +70,21 @@ JS_DEVICE void tmem_st_32x32(uint32_t taddr, const uint32_t* r) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// Bounded wait that backs off between polls: the waiting roles share the SM's load/store path with the
+// loaders' cp.async traffic, so they must not spin on it.
+JS_DEVICE bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < (kSpinLimit >> 2); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    __nanosleep(20);
+  }
+  report(status, code);
+  return false;
+}
+JS_DEVICE float fast_exp2(float x) {     // 2^x, flushing denormal results to zero; exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 JS_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // MN-major operand tile stored as two 64-element halves of 128-byte rows (8-row groups 1024 B apart,
@@ -83,6 +100,16 @@ JS_DEVICE uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t half_stride) 
 }
 JS_DEVICE constexpr uint32_t umma_idesc_bf16_bmn(int M, int N) {   // B operand MN-major
   return umma_idesc_bf16(M, N) | (1u << 16);
+}
+
+// Optional phase trace (nanosecond timestamps written by CTA (0,0,0)); null unless a profiling script sets it.
+__device__ unsigned long long* g_attn_trace = nullptr;
+JS_DEVICE void attn_trace(int slot) {
+  if (g_attn_trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_attn_trace[slot] = t;
+  }
 }
 
 template <int G>
@@ -108,6 +135,7 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
 
   pdl_launch_dependents();
   pdl_wait();
+  if (tid == 0) attn_trace(0);
 
   // ---- which sequence does this q tile belong to (same numbering as the mma.sync kernel)
   int lo = 0, hi = p.B - 1;
@@ -135,7 +163,10 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
   const bool row_valid = node < n_b;
   const size_t out_row = static_cast<size_t>(q_begin + (row_valid ? node : 0)) * p.Hq + head;
 
-  if (nt <= 0) {   // more splits than key tiles: this split contributes nothing
+  const bool cmerge = p.cluster_merge != 0;
+  float m_run = -INFINITY, l_run = 0.f;     // softmax threads: running (integer) maximum and sum of their row
+  bool sm_ok = true;
+  if (nt <= 0 && !cmerge) {   // more splits than key tiles: this split contributes nothing
     if (warp < 4 && row_valid && p.splits > 1) {
       float* ml = p.ws_ml + (static_cast<size_t>(split) * p.T * p.Hq + out_row) * 2;
       ml[0] = -INFINITY;
@@ -144,28 +175,32 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
     return;
   }
 
-  if (tid == 0) {
-    mbar_init(q_full, 128);
-    for (int s = 0; s < TSTAGES; ++s) { mbar_init(&kv_full[s], 128); mbar_init(&kv_empty[s], 1); }
+  if (tid == 0 && nt > 0) {
+    mbar_init(q_full, TLOADERS);
+    for (int s = 0; s < TSTAGES; ++s) { mbar_init(&kv_full[s], TLOADERS); mbar_init(&kv_empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128); mbar_init(&pv_done[i], 1); }
     mbar_init(o_done, 1);
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == 4 && nt > 0) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = nt > 0 ? *tmem_slot : 0u;
+  if (tid == 0) attn_trace(1);      // setup done
   const uint32_t tmem_o = tmem_base + 128;      // S buffers at columns [0,64) and [64,128)
 
-  if (warp >= 5) {
-    // ================================================================ loaders (128 threads)
+  const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  if (nt <= 0) {
+    // (cluster merge) nothing to compute: this CTA only takes part in the exchange below
+  } else if (warp >= 5) {
+    // ================================================================ loaders
     const int lt = tid - 160;
     const uint32_t q_addr = smem_u32(sQ);
-    for (int c = lt; c < TROWS * 16; c += 128) {
+    for (int c = lt; c < TROWS * 16; c += TLOADERS) {
       const int r = c >> 4, ch = c & 15;
       const int nd = node0 + r / G;
       const bool valid = nd < n_b;
@@ -173,7 +208,15 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
       cp_async16_tc(q_addr + (ch >> 3) * (TROWS * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4), src, valid);
     }
     cp_async_commit_tc();
-    const int ch = lt & 15, r0 = lt >> 4;       // this thread copies chunk `ch` of keys r0, r0+8, ...
+    constexpr int RSTEP = TLOADERS / 16;        // key rows covered by one pass of all loader threads
+    const int ch = lt & 15, r0 = lt >> 4;       // this thread copies chunk `ch` of keys r0, r0+RSTEP, ...
+    // slots of the first tile; the next tile's are fetched while the current tile's copies are issued
+    int slot_next[TKEYS / RSTEP];
+#pragma unroll
+    for (int j = 0; j < TKEYS / RSTEP; ++j) {
+      const int kp = t_begin * TKEYS + r0 + RSTEP * j;
+      slot_next[j] = kp < L ? __ldg(slots + kp) : 0;
+    }
     bool ok = true;
     // copies complete in issue order (Q, tile 0, tile 1, ...); `next_sig` is the next one to publish (-1 = Q)
     int next_sig = -1;
@@ -181,28 +224,36 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
       if (next_sig < upto) fence_proxy_async();
       for (; next_sig < upto; ++next_sig) {
         if (next_sig < 0) mbar_arrive(q_full); else mbar_arrive(&kv_full[next_sig % TSTAGES]);
+        if (lt == 0 && next_sig >= 0 && next_sig < 8) attn_trace(40 + next_sig);   // tile published by loader thread 0
       }
     };
     for (int i = 0; i < nt && ok; ++i) {
       const int s = i % TSTAGES;
       if (i >= TSTAGES) {
         const uint32_t par = ((i / TSTAGES) & 1) ^ 1;
-        if (!mbar_try_wait(&kv_empty[s], par)) {
+        if (!mbar_test_wait(&kv_empty[s], par)) {
           // about to block on the consumer: it may itself be waiting for tiles not yet published
           cp_async_wait_tc<0>();
           publish_before(i);
-          ok = mbar_wait(&kv_empty[s], par, p.status, kTimeoutEmpty);
+          ok = mbar_wait_backoff(&kv_empty[s], par, p.status, kTimeoutEmpty);
         }
       }
       if (!ok) break;
       const int k0 = (t_begin + i) * TKEYS;
       const uint32_t k_addr = smem_u32(sKV + s * kStageKV);
+      int slot_cur[TKEYS / RSTEP];
 #pragma unroll
-      for (int j = 0; j < TKEYS / 8; ++j) {
-        const int r = r0 + 8 * j;
+      for (int j = 0; j < TKEYS / RSTEP; ++j) {
+        slot_cur[j] = slot_next[j];
+        const int kpn = k0 + TKEYS + r0 + RSTEP * j;
+        slot_next[j] = (i + 1 < nt && kpn < L) ? __ldg(slots + kpn) : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < TKEYS / RSTEP; ++j) {
+        const int r = r0 + RSTEP * j;
         const int kp = k0 + r;
         const bool valid = kp < L;
-        int slot = valid ? __ldg(slots + kp) : 0;
+        int slot = slot_cur[j];
         if (slot < 0 || slot >= p.S) { report(p.status, kBadSlot); slot = 0; }
         const size_t off = (static_cast<size_t>(h) * p.S + slot) * TD + ch * 8;
         const uint32_t dst = (ch >> 3) * (TKEYS * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
@@ -210,6 +261,7 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
         cp_async16_tc(k_addr + TKEYS * 256 + dst, p.v_pool + off, valid);
       }
       cp_async_commit_tc();
+      if (lt == 0 && i < 8) attn_trace(32 + i);    // copies of tile i issued
       cp_async_wait_tc<2>();          // everything but the two newest groups has landed
       publish_before(i - 1);
     }
@@ -222,7 +274,8 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(TROWS, TKEYS);
       constexpr uint32_t idesc_pv = umma_idesc_bf16_bmn(TROWS, TD);
-      bool ok = mbar_wait(q_full, 0, p.status, kTimeoutFull);
+      bool ok = mbar_wait_backoff(q_full, 0, p.status, kTimeoutFull);
+      attn_trace(2);                // Q landed
       auto issue_pv = [&](int j) {
         const int s = j % TSTAGES, pb = j & 1;
         const uint32_t v_addr = smem_u32(sKV + s * kStageKV + TKEYS * 256);
@@ -235,8 +288,9 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
       };
       for (int i = 0; i < nt && ok; ++i) {
         const int s = i % TSTAGES, sb = i & 1;
-        ok = mbar_wait(&kv_full[s], (i / TSTAGES) & 1, p.status, kTimeoutFull);
+        ok = mbar_wait_backoff(&kv_full[s], (i / TSTAGES) & 1, p.status, kTimeoutFull);
         if (!ok) break;
+        if (i < 8) attn_trace(8 + i);   // K/V tile i landed
         // S buffer sb was consumed when P of tile i-2 was published (waited for below, before PV(i-2))
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sKV + s * kStageKV);
@@ -248,14 +302,14 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
         }
         umma_commit(&s_full[sb]);
         if (i >= 1) {
-          ok = mbar_wait(&p_full[(i - 1) & 1], ((i - 1) >> 1) & 1, p.status, kTimeoutAccum);
+          ok = mbar_wait_backoff(&p_full[(i - 1) & 1], ((i - 1) >> 1) & 1, p.status, kTimeoutAccum);
           if (!ok) break;
           tc_fence_after();
           issue_pv(i - 1);
         }
       }
       if (ok) {
-        ok = mbar_wait(&p_full[(nt - 1) & 1], ((nt - 1) >> 1) & 1, p.status, kTimeoutAccum);
+        ok = mbar_wait_backoff(&p_full[(nt - 1) & 1], ((nt - 1) >> 1) & 1, p.status, kTimeoutAccum);
         if (ok) {
           tc_fence_after();
           issue_pv(nt - 1);
@@ -265,18 +319,17 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
     }
   } else {
     // ================================================================ softmax + epilogue (one row per thread)
-    const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
     int mw[8];
 #pragma unroll
     for (int w = 0; w < 8; ++w)
       mw[w] = (!p.causal && row_valid && w < p.W) ? p.mask_bits[static_cast<size_t>(q_begin + node) * p.W + w] : 0;
-    float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int i = 0; i < nt && ok; ++i) {
       const int sb = i & 1;
-      ok = mbar_wait(&s_full[sb], (i >> 1) & 1, p.status, kTimeoutAccum);
+      ok = mbar_wait_backoff(&s_full[sb], (i >> 1) & 1, p.status, kTimeoutAccum);
       if (!ok) break;
       tc_fence_after();
+      if (tid == 0 && i < 8) attn_trace(16 + i);   // scores of tile i ready
       uint32_t sr[64];
       tmem_ld_32x32(tmem_base + t_lane + sb * TKEYS, sr);
       tmem_ld_32x32(tmem_base + t_lane + sb * TKEYS + 32, sr + 32);
@@ -306,14 +359,24 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
         const int left = L - k0;                         // keys at or past L do not exist
         if (left < 64) vm &= (left <= 0) ? 0ull : ((1ull << left) - 1ull);
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one 64-deep
+      if (vm == ~0ull) {              // the common case: every key of the tile is visible to this row
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const bool vis = (vm >> c) & 1ull;
-        const float x = vis ? __uint_as_float(sr[c]) * p.scale_log2 : -INFINITY;
-        sr[c] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
+        for (int c = 0; c < 64; ++c) {
+          const float x = __uint_as_float(sr[c]) * p.scale_log2;
+          sr[c] = __float_as_uint(x);
+          mx4[c & 3] = fmaxf(mx4[c & 3], x);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const bool vis = (vm >> c) & 1ull;
+          const float x = vis ? __uint_as_float(sr[c]) * p.scale_log2 : -INFINITY;
+          sr[c] = __float_as_uint(x);
+          mx4[c & 3] = fmaxf(mx4[c & 3], x);
+        }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // integer running maximum in the log2 domain (probabilities are then exact powers of two apart
       // whatever the tile order or key split; see the mma.sync kernel)
       const float m_new = fmaxf(m_run, ceilf(mx));
@@ -321,29 +384,29 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
       const float alpha = exp2f(m_run - m_safe);          // 0 when nothing was visible before
       m_run = m_new;
       // P buffer sb is free once PV of tile i-2 has completed
-      if (i >= 2) ok = mbar_wait(&pv_done[sb], ((i - 2) >> 1) & 1, p.status, kTimeoutAccum);
+      if (i >= 2) ok = mbar_wait_backoff(&pv_done[sb], ((i - 2) >> 1) & 1, p.status, kTimeoutAccum);
       if (!ok) break;
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       const uint32_t p_row = smem_u32(sP + sb * kSmemP) + row * 128;
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
         uint32_t w4[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(__uint_as_float(sr[c8 * 8 + 2 * e]) - m_safe);
-          const float p1 = exp2f(__uint_as_float(sr[c8 * 8 + 2 * e + 1]) - m_safe);
-          rs += p0 + p1;
+          const float p0 = fast_exp2(__uint_as_float(sr[c8 * 8 + 2 * e]) - m_safe);
+          const float p1 = fast_exp2(__uint_as_float(sr[c8 * 8 + 2 * e + 1]) - m_safe);
+          rs4[e] += p0 + p1;
           __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
           w4[e] = *reinterpret_cast<uint32_t*>(&v);
         }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)), "r"(w4[0]),
                      "r"(w4[1]), "r"(w4[2]), "r"(w4[3]) : "memory");
       }
-      l_run = l_run * alpha + rs;
+      l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       // rescale O when some row of this warp raised its maximum (tcgen05.ld/st are warp-wide)
       const bool need = i > 0 && alpha != 1.f;
       if (__any_sync(0xffffffffu, need)) {
-        ok = mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, p.status, kTimeoutAccum);   // every earlier PV is in O
+        ok = mbar_wait_backoff(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, p.status, kTimeoutAccum);   // every earlier PV is in O
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
@@ -360,11 +423,14 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
       fence_proxy_async();          // P (generic-proxy stores) -> visible to the MMA's async-proxy reads
       tc_fence_before();
       mbar_arrive(&p_full[sb]);
+      if (tid == 0 && i < 8) attn_trace(24 + i);   // P of tile i published
     }
     // ---- epilogue
-    if (ok) ok = mbar_wait(o_done, 0, p.status, kTimeoutAccum);
+    if (ok) ok = mbar_wait_backoff(o_done, 0, p.status, kTimeoutAccum);
     tc_fence_after();
-    if (ok) {
+    if (tid == 0) attn_trace(3);    // output accumulator complete
+    sm_ok = ok;
+    if (ok && !cmerge) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < TD; c0 += 32) {
@@ -397,10 +463,81 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
     }
   }
 
+  if (cmerge) {
+    // ---------------------------------------------------------------- merge of the key splits inside the cluster
+    // Column chunk c (32 of the 128 output columns) is finished by CTA c % splits.  Every CTA pushes its
+    // unnormalised chunk (column-major, 16 KB) into the owner's shared memory and its rows' (max, sum) to
+    // all CTAs; the receive area reuses the K/V stages, which are dead once every CTA has left its main loop.
+    const int per_owner = (4 + p.splits - 1) / p.splits;
+    float* recv_o = reinterpret_cast<float*>(sKV);
+    float* recv_ml = recv_o + p.splits * per_owner * 4096;
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (tid == 0) attn_trace(5);    // every CTA of the cluster left its main loop
+    if (warp < 4) {
+      const bool have = nt > 0 && sm_ok;
+      const float m_pub = have ? m_run : -INFINITY;
+      const uint32_t ml_addr = smem_u32(recv_ml) + static_cast<uint32_t>((split * TROWS + row) * 8);
+      for (int d = 0; d < p.splits; ++d) {
+        const uint32_t a = map_to_cta(ml_addr, d);
+        st_dsmem_f32(a, m_pub);
+        st_dsmem_f32(a + 4, have ? l_run : 0.f);
+      }
+      if (have) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orr[32];
+          tmem_ld_32x32(tmem_o + t_lane + c * 32, orr);
+          tmem_ld_wait();
+          const uint32_t dst = map_to_cta(smem_u32(recv_o), c % p.splits) +
+                               static_cast<uint32_t>(((split * per_owner + c / p.splits) * 4096 + row) * 4);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st_dsmem_f32(dst + j * (TROWS * 4), __uint_as_float(orr[j]));
+        }
+      }
+    }
+    if (tid == 0) attn_trace(6);    // partials pushed
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (tid == 0) attn_trace(7);    // partials of all splits landed
+    if (warp < 4 && row_valid) {
+      float m = -INFINITY;
+      for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, recv_ml[(s2 * TROWS + row) * 2]);
+      float wsrc[8], lsum = 0.f;
+      for (int s2 = 0; s2 < p.splits; ++s2) {
+        const float ms = recv_ml[(s2 * TROWS + row) * 2];
+        wsrc[s2] = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+        lsum += recv_ml[(s2 * TROWS + row) * 2 + 1] * wsrc[s2];
+      }
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      for (int c = split; c < 4; c += p.splits) {
+        float acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+        for (int s2 = 0; s2 < p.splits; ++s2) {
+          if (wsrc[s2] == 0.f) continue;       // that split saw no visible key (its chunk was never pushed)
+          const float* src = recv_o + (s2 * per_owner + c / p.splits) * 4096 + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] += src[j * TROWS] * wsrc[s2];
+        }
+        uint4 pk[4];
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(pk);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j] * inv, acc[2 * j + 1] * inv);
+        uint4* dst = reinterpret_cast<uint4*>(p.out + out_row * TD + c * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = pk[j];
+      }
+    }
+  }
+
   // ------------------------------------------------------------------ teardown
+  if (tid == 0) attn_trace(4);      // epilogue stores issued
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 4 && nt > 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
@@ -419,15 +556,31 @@ static int launch_attn_tc(const AttnTcParams& p, int q_tiles, bool pdl, cudaStre
   cfg.blockDim = dim3(TTHREADS);
   cfg.dynamicSmemBytes = kAttnTcSmem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.cluster_merge) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = p.splits;
+    ++na;
+  }
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace js
+
+// Profiling hook: 32 timestamps of CTA (0,0,0) go to `buf` (device memory) on every launch; nullptr switches it off.
+extern "C" int js_attn_tc_set_trace(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(js::g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -1;
+}
 
 extern "C" int js_attn_merge(float* ws_o, float* ws_ml, void* out, int T, int Hq, int splits, int pdl, cudaStream_t stream);
 
@@ -447,7 +600,7 @@ extern "C" int js_paged_tree_attention_tc(const void* q, const void* k_pool, con
   AttnTcParams p{reinterpret_cast<const __nv_bfloat16*>(q), reinterpret_cast<const __nv_bfloat16*>(k_pool),
                  reinterpret_cast<const __nv_bfloat16*>(v_pool), slot_map, seq_rows, cu_q, past_lens, mask_bits,
                  reinterpret_cast<__nv_bfloat16*>(out), ws_o, ws_ml, status, B, T, Hq, Hkv, S, max_len, W, causal,
-                 splits, scale * 1.4426950408889634f};
+                 splits, scale * 1.4426950408889634f, (splits == 2 || splits == 4) ? 1 : 0};
   int rc;
   switch (G) {
     case 1: rc = launch_attn_tc<1>(p, (T + 127) / 128 + B, pdl != 0, stream); break;
@@ -457,6 +610,6 @@ extern "C" int js_paged_tree_attention_tc(const void* q, const void* k_pool, con
     case 16: rc = launch_attn_tc<16>(p, (T + 7) / 8 + B, pdl != 0, stream); break;
     default: return -14;
   }
-  if (rc != 0 || splits == 1) return rc;
+  if (rc != 0 || splits == 1 || p.cluster_merge) return rc;
   return js_attn_merge(ws_o, ws_ml, out, T, Hq, splits, pdl, stream);
 }

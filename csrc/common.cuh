@@ -58,6 +58,18 @@ JS_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test (try_wait may suspend the thread for microseconds before answering "not yet").
+JS_DEVICE bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait; false on timeout (status gets `code`).
 JS_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {

@@ -150,6 +150,9 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
     scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
     last = len(layers) - 1
     n = 0
+    # the split merge is a second launch unless the tcgen05 kernel does it inside a cluster (2 or 4 splits)
+    in_kernel = X.attn_impl(Hq, Hkv, 0 if mask_bits is None else mask_bits.shape[1]) == "tc" and st.splits in (2, 4)
+    merge_launch = 1 if st.splits > 1 and not in_kernel else 0
     for li, L in enumerate(layers):
         def attend(li=li, L=L):
             X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps,
@@ -157,7 +160,7 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits,
                                    scale, causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
         if L.get("fp4"):
-            n += _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) + 2 + (1 if st.splits > 1 else 0)
+            n += _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) + 2 + merge_launch
             if taps is not None and li != last:
                 for j, t in enumerate(tap_ids):
                     if t == li:
@@ -177,7 +180,7 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
         else:
             tp.gemm_allreduce(st.act, L["down"], st.x, residual=st.x, pdl=pdl)
-        n += 8 + (1 if st.splits > 1 else 0)
+        n += 8 + merge_launch
         if taps is not None and li != last:
             for j, t in enumerate(tap_ids):
                 if t == li:

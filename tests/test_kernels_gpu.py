@@ -136,7 +136,7 @@ def _random_tree_bits(n, words, rng):
 
 
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (8, 1), (4, 4)])
-@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4])     # 2 and 4 merge inside a cluster on the tcgen05 kernel
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("impl", ["mma", "tc"])
 def test_paged_tree_attention(ext, Hq, Hkv, splits, causal, impl):
