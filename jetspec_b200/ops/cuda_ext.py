@@ -264,13 +264,15 @@ def quant_nvfp4(x: torch.Tensor, buf: Optional[dict] = None, norm_w: Optional[to
 
 
 def pick_nvfp4_split(M: int, N: int, K: int, epi: int) -> int:
+    """K split for the NVFP4 GEMM: same placement rule as the bf16 kernel (clusters of 4 / 2 that fit one wave)."""
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     kb = K // 256
     max_split = 2 if epi == EPI_SWIGLU else 4
-    split = 1
-    while split < max_split and tiles * (split + 1) <= SM_COUNT and kb // (split + 1) >= 2:
-        split += 1
-    return split
+    room = {2: 72, 4: 32}
+    for c in (4, 2):
+        if c <= max_split and tiles <= room[c] and tiles * c <= SM_COUNT and kb // c >= 2:
+            return c
+    return 1
 
 
 def gemm_nvfp4(x, qw, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
