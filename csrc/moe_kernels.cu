@@ -1,0 +1,163 @@
+// MoE routing on the device: softmax over the experts + top-k (+ renormalisation), then the stable
+// permutation of the (token, choice) pairs by local expert that the grouped GEMMs consume.
+//
+// Counterpart of the reference's router path (jetspec/models/moe_fused.py:16-51: softmax, topk, renorm,
+// argsort by expert); here two kernels, no host synchronisation, static output shapes (graph-capturable):
+//   route:  one warp per token, k rounds of a warp-wide argmax over the token's probabilities
+//   sort:   one CTA; shared-memory histogram (integer atomics: counts are exact), scan, and a stable
+//           placement where each key's pairs are ranked with warp ballots in pair order
+#include "common.cuh"
+
+#include <math.h>
+
+namespace js {
+
+constexpr int kMaxExpertsPerLane = 8;     // experts <= 256
+constexpr int kSortThreads = 1024;
+constexpr int kSortMaxPairs = 16384;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
+                                 float* __restrict__ wts, int* __restrict__ idx) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  float v[kMaxExpertsPerLane];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    v[i] = (lane + 32 * i) < E ? expf(v[i] - mx) : -1.f;    // -1 marks "not an expert"
+    sum += fmaxf(v[i], 0.f);
+  }
+  sum = warp_sum(sum);
+  float kept = 0.f;
+  float my_w = 0.f;
+  int my_e = 0;
+  for (int j = 0; j < k; ++j) {
+    // warp argmax; ties go to the lower expert index
+    float best = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > best) { best = v[i]; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if ((be & 31) == lane) v[be >> 5] = -1.f;      // remove the winner
+    kept += best;
+    if (lane == j) { my_w = best; my_e = be; }
+  }
+  if (lane < k) {
+    const float p = my_w / sum;
+    wts[static_cast<size_t>(t) * k + lane] = renorm ? p / (kept / sum) : p;
+    idx[static_cast<size_t>(t) * k + lane] = my_e;
+  }
+}
+
+// pairs p = t*k + j with expert idx[p]; key = local expert (idx - first) or n_local for other ranks' experts
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int P, int E, int first, int n_local,
+                int* __restrict__ order, float* __restrict__ row_weight, int* __restrict__ group_off,
+                int* __restrict__ counts_all) {
+  extern __shared__ int sh[];
+  int* key = sh;                       // P
+  int* cnt = key + P;                  // n_local + 1
+  int* off = cnt + n_local + 1;        // n_local + 2
+  int* call = off + n_local + 2;       // E
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) cnt[i] = 0;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) call[i] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = idx[p];
+    const int l = e - first;
+    const int kk = (l >= 0 && l < n_local) ? l : n_local;
+    key[p] = kk;
+    atomicAdd(&cnt[kk], 1);
+    if (e >= 0 && e < E) atomicAdd(&call[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int i = 0; i <= n_local; ++i) { off[i] = run; run += cnt[i]; }
+    off[n_local + 1] = run;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) group_off[i] = off[i];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) counts_all[i] = call[i];
+  // stable placement: warp w ranks the pairs of keys w, w + warps, ...
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int kk = warp; kk <= n_local; kk += warps) {
+    int base = off[kk];
+    for (int p0 = 0; p0 < P; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < P && key[p] == kk;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int pos = base + __popc(m & ((1u << lane) - 1u));
+        order[pos] = p;
+        row_weight[pos] = wts[p];
+      }
+      base += __popc(m);
+    }
+  }
+}
+
+}  // namespace js
+
+// logits (T, E) fp32 -> wts (T, k) fp32, idx (T, k) int32.  E <= 256, k <= 32.
+extern "C" int js_moe_route(const float* logits, int T, int E, int k, int renorm, float* wts, int* idx, int pdl,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 32 * js::kMaxExpertsPerLane || k < 1 || k > 32 || k > E) return -10;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3((T + 7) / 8);
+  c.blockDim = dim3(256);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::moe_route_kernel, logits, T, E, k, renorm, wts, idx) == cudaSuccess ? 0 : -4;
+}
+
+// idx / wts (P = T*k) -> order (P), row_weight (P), group_off (n_local + 1), counts_all (E).
+extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int first, int n_local, int* order,
+                           float* row_weight, int* group_off, int* counts_all, int pdl, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (P > js::kSortMaxPairs || n_local < 1 || E < 1) return -10;
+  const int smem = (P + 2 * n_local + 3 + E) * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(js::moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured = smem;
+  }
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(js::kSortThreads);
+  c.dynamicSmemBytes = smem;
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::moe_sort_kernel, idx, wts, P, E, first, n_local, order, row_weight, group_off,
+                            counts_all) == cudaSuccess ? 0 : -4;
+}

@@ -50,8 +50,16 @@ class DenseKVCache:
         This is the physical compaction of the accepted path
         (reference: ``_select_kv_cache``, ``jetspec/core/llm.py:86-112``).
         """
+        n = len(keep_tree_indices)
+        if (n and n <= 64 and self.k[0].is_cuda and self.k[0].dtype == torch.bfloat16 and self.k[0].shape[-1] == 128
+                and self.k[0].is_contiguous()):
+            from ..ops import cuda_ext as X                   # compaction kernel (rows staged in shared memory)
+            keep = torch.as_tensor(keep_tree_indices, dtype=torch.int32).to(self.device)
+            for i in range(len(self.k)):
+                X.kv_compact(self.k[i], self.v[i], past_len, keep)
+            self.length = past_len + n
+            return
         idx = torch.as_tensor(keep_tree_indices, dtype=torch.long, device=self.device) + past_len
-        n = idx.numel()
         for i in range(len(self.k)):
             self.k[i][:, past_len:past_len + n] = self.k[i][:, idx]
             self.v[i][:, past_len:past_len + n] = self.v[i][:, idx]

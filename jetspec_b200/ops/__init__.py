@@ -13,7 +13,15 @@ import torch
 
 from . import reference as ref
 from .reference import (pack_ancestor_bits, unpack_ancestor_bits, rope_cos_sin, apply_rope,
-                        moe_route, sample)
+                        moe_route)
+
+
+def sample(logits, temperature: float = 0.0, generator=None):
+    """argmax at temperature 0, else one draw per row from ``softmax(logits / T)``; CUDA tensors use the
+    sampling kernel (the generator must then be a CUDA generator or None)."""
+    if temperature >= 1e-5 and logits.is_cuda and (generator is None or generator.device.type == "cuda"):
+        return _ext().sample_temperature(logits, temperature, generator)
+    return ref.sample(logits, temperature, generator)
 
 
 def _kern(x: torch.Tensor) -> bool:

@@ -465,6 +465,65 @@ def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
     return out
 
 
+# ------------------------------------------------------------------ routing, sampling, compaction
+def moe_route(router_logits: torch.Tensor, top_k: int, renorm: bool, pdl: bool = False):
+    """``(weights (T, k) fp32, experts (T, k) int32)``: softmax over the experts, top-k, optional renormalisation."""
+    lib = load()
+    lg = router_logits.float().contiguous()
+    T, E = lg.shape
+    wts = torch.empty(T, top_k, dtype=torch.float32, device=lg.device)
+    idx = torch.empty(T, top_k, dtype=torch.int32, device=lg.device)
+    lib.js_moe_route.restype = ctypes.c_int
+    _check(lib.js_moe_route(_p(lg), T, E, top_k, int(bool(renorm)), _p(wts), _p(idx), int(pdl), _stream()), "js_moe_route")
+    return wts, idx
+
+
+def moe_route_sort(router_logits: torch.Tensor, top_k: int, renorm: bool, first_expert: int, n_local: int,
+                   pdl: bool = False):
+    """Routing plus the stable permutation of the (token, choice) pairs by local expert, all on the device.
+    Returns ``(order int32 (T*k), row_weight fp32 (T*k), group_off int32 (n_local+1), counts_all int32 (E))``."""
+    lib = load()
+    wts, idx = moe_route(router_logits, top_k, renorm, pdl)
+    T, E = router_logits.shape
+    P = T * top_k
+    dev = wts.device
+    order = torch.empty(P, dtype=torch.int32, device=dev)
+    row_w = torch.empty(P, dtype=torch.float32, device=dev)
+    group_off = torch.empty(n_local + 1, dtype=torch.int32, device=dev)
+    counts_all = torch.empty(E, dtype=torch.int32, device=dev)
+    lib.js_moe_sort.restype = ctypes.c_int
+    _check(lib.js_moe_sort(_p(idx), _p(wts), P, E, int(first_expert), int(n_local), _p(order), _p(row_w), _p(group_off),
+                           _p(counts_all), int(pdl), _stream()), "js_moe_sort")
+    return order, row_w, group_off, counts_all
+
+
+def sample_temperature(logits: torch.Tensor, temperature: float, generator=None) -> torch.Tensor:
+    """Draw one token per row from ``softmax(logits / temperature)`` (inverse CDF with one uniform per row)."""
+    lib = load()
+    shp = logits.shape[:-1]
+    flat = logits.reshape(-1, logits.shape[-1])
+    if flat.dtype not in (torch.float32, torch.bfloat16):
+        flat = flat.float()
+    flat = flat.contiguous()
+    N, V = flat.shape
+    u = torch.rand(N, dtype=torch.float32, device=flat.device, generator=generator)
+    out = torch.empty(N, dtype=torch.int64, device=flat.device)
+    lib.js_sample_temperature.restype = ctypes.c_int
+    _check(lib.js_sample_temperature(_p(flat), int(flat.dtype == torch.bfloat16), N, V, flat.stride(0),
+                                     ctypes.c_float(temperature), _p(u), _p(out), _stream()), "js_sample_temperature")
+    return out.view(shp)
+
+
+def kv_compact(k: torch.Tensor, v: torch.Tensor, past_len: int, keep: torch.Tensor) -> None:
+    """In place: positions ``past_len + i`` of ``k, v (Hkv, capacity, 128)`` take the rows ``past_len + keep[i]``."""
+    lib = load()
+    assert k.dtype == torch.bfloat16 and k.shape[-1] == 128 and k.is_contiguous() and v.is_contiguous()
+    keep = keep.to(device=k.device, dtype=torch.int32).contiguous()
+    lib.js_kv_compact.restype = ctypes.c_int
+    _check(lib.js_kv_compact(_p(k), _p(v), k.shape[0], k.shape[1], int(past_len), _p(keep), keep.numel(), _stream()),
+           "js_kv_compact")
+
+
 # ------------------------------------------------------------------ MoE (grouped through the dense GEMM)
 _moe_cache: dict = {}
 

@@ -42,8 +42,13 @@ def route_and_sort(router_logits: torch.Tensor, top_k: int, renorm: bool, first_
     weights, ``group_off (n_local+1,)`` the row ranges of the local experts, ``counts_all (E,)`` the
     global per-expert pair counts (identical on every rank).
     """
-    wts, idx = ref.moe_route(router_logits, top_k, renorm)
     E = router_logits.shape[-1]
+    if router_logits.is_cuda and E <= 256 and router_logits.shape[0] * top_k <= 16384:
+        # router + permutation kernels (no host synchronisation, static shapes)
+        from ..ops import cuda_ext as X
+        order, row_w, group_off, counts_all = X.moe_route_sort(router_logits, top_k, renorm, first_expert, n_local)
+        return order.long(), row_w, group_off, counts_all.long()
+    wts, idx = ref.moe_route(router_logits, top_k, renorm)
     flat_e = idx.reshape(-1)
     local = flat_e - first_expert
     key = torch.where((local >= 0) & (local < n_local), local, torch.full_like(local, n_local))

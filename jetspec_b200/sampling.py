@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from .ops.reference import sample  # noqa: F401  (re-export)
+from .ops import sample  # noqa: F401  (re-export)
 
 
 @dataclass

@@ -255,3 +255,54 @@ def test_grouped_moe_matches_reference(ext, T):
     torch.cuda.synchronize()
     assert rel_err(out, exp) < 2 * BF16_TOL
     ext.check_status("cuda")
+
+
+@pytest.mark.parametrize("T,E,k,renorm", [(96, 128, 8, True), (5, 16, 4, False), (1024, 128, 8, True)])
+def test_moe_route_and_sort_kernels(ext, T, E, k, renorm):
+    from jetspec_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g, device="cuda") * 2
+    w_ref, i_ref = ref.moe_route(logits, k, renorm)
+    w, i = ext.moe_route(logits, k, renorm)
+    assert torch.equal(i.long(), i_ref)
+    assert float((w - w_ref).abs().max()) < 1e-6
+    first, n_local = E // 4, E // 2                       # this "rank" owns the middle half of the experts
+    order, row_w, group_off, counts_all = ext.moe_route_sort(logits, k, renorm, first, n_local)
+    flat = i_ref.reshape(-1)
+    local = flat - first
+    key = torch.where((local >= 0) & (local < n_local), local, torch.full_like(local, n_local))
+    exp_order = torch.argsort(key, stable=True)
+    assert torch.equal(order.long(), exp_order)
+    assert float((row_w - w_ref.reshape(-1)[exp_order]).abs().max()) < 1e-6
+    assert torch.equal(group_off[1:].long(), torch.bincount(key, minlength=n_local + 1)[:n_local].cumsum(0))
+    assert int(group_off[0]) == 0
+    assert torch.equal(counts_all.long(), torch.bincount(flat, minlength=E))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sample_temperature_kernel(ext, dtype):
+    N, V, T = 64, 151936, 0.7
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = (torch.randn(N, V, generator=g, device="cuda") * 3).to(dtype)
+    gs = torch.Generator(device="cuda").manual_seed(11)
+    out = ext.sample_temperature(logits, T, gs)
+    u = torch.rand(N, dtype=torch.float32, device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+    cdf = torch.softmax(logits.double() / T, -1).cumsum(-1)
+    hi = cdf.gather(1, out[:, None]).squeeze(1)
+    lo = torch.where(out > 0, cdf.gather(1, (out - 1).clamp_min(0)[:, None]).squeeze(1), torch.zeros_like(hi))
+    assert bool(((u.double() >= lo - 1e-5) & (u.double() <= hi + 1e-5)).all())       # inverse CDF of the same uniforms
+    cold = ext.sample_temperature(logits, 1e-3, gs)                                    # T -> 0: the arg max
+    top = logits.float().max(-1).values                                                # (bf16 logits have tied maxima)
+    assert torch.equal(logits.float().gather(1, cold[:, None]).squeeze(1), top)
+
+
+def test_kv_compact_kernel(ext):
+    Hkv, cap, D, past = 4, 300, 128, 37
+    k, v = rnd(Hkv, cap, D, seed=31), rnd(Hkv, cap, D, seed=32)
+    keep = torch.tensor([0, 2, 3, 9, 10, 40], dtype=torch.int32)     # overlapping source and destination ranges
+    k0, v0 = k.clone(), v.clone()
+    ext.kv_compact(k, v, past, keep)
+    torch.cuda.synchronize()
+    idx = keep.long().cuda() + past
+    assert torch.equal(k[:, past:past + 6], k0[:, idx]) and torch.equal(v[:, past:past + 6], v0[:, idx])
+    assert torch.equal(k[:, :past], k0[:, :past]) and torch.equal(k[:, past + 6:], k0[:, past + 6:])
