@@ -49,14 +49,14 @@ def main():
         if only and name not in only.split(","):
             continue
         size = N * K * 2
-        R = max(4, (400 << 20) // size + 1)
+        R = int(os.environ.get("COPIES", 0)) or max(4, (400 << 20) // size + 1)     # COPIES=1: weights stay in L2
         ws = [(torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(R)]
         x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         out = torch.empty(M, N // (2 if epi == 1 else 1), device="cuda", dtype=torch.bfloat16)
         full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         res = {"cublas": round(chain_time(lambda i: torch.matmul(x, ws[i].t(), out=full), R), 1),
                "picked": round(chain_time(lambda i: X.gemm(x, ws[i], out=out, epi=epi, pdl=True), R), 1)}
-        for deep in (0, 2, 1):
+        for deep in ((0, 2, 1) if not os.environ.get("PICKED_ONLY") else ()):
             for split in (1, 2, 3, 4):
                 for pdl in (0, 1):
                     try:

@@ -120,3 +120,27 @@ extern "C" int js_kv_compact(void* k, void* v, int Hkv, int capacity, int past, 
                                                    capacity, past, keep, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------- weight prefetch into L2
+// Decode rounds leave HBM idle while attention, norms and the GEMM prologues/epilogues run.  This kernel,
+// launched on a side stream, asks the memory system to pull the NEXT GEMM's weights into L2
+// (cp.async.bulk.prefetch.L2) so that GEMM finds them there; it only issues requests and exits.
+namespace js {
+__global__ void l2_prefetch_kernel(const uint8_t* base, size_t bytes, uint32_t chunk) {
+  const size_t n = (bytes + chunk - 1) / chunk;
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t off = i * chunk;
+    const uint32_t sz = static_cast<uint32_t>(bytes - off < chunk ? bytes - off : chunk) & ~15u;
+    if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
+  }
+}
+}  // namespace js
+
+// Prefetch `bytes` (rounded down to 16) starting at the 16-byte aligned `ptr` into L2.
+extern "C" int js_l2_prefetch(const void* ptr, size_t bytes, int ctas, cudaStream_t stream) {
+  if (bytes < 16) return 0;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return -11;
+  if (ctas < 1) ctas = 8;
+  js::l2_prefetch_kernel<<<ctas, 128, 0, stream>>>(reinterpret_cast<const uint8_t*>(ptr), bytes, 8192u);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -32,6 +32,10 @@ from ..tree.builder import topk_rows
 
 ST_PAST, ST_CTX, ST_NEW, ST_DONE, ST_GEN, ST_NNODES, ST_ROUNDS = range(7)
 _PDL = os.environ.get("JETSPEC_PDL", "1") != "0"
+# Off by default: measured slower (5.68 -> 6.5 ms/round at best).  The decoder GEMMs at 128 rows are bound by
+# their per-launch latency chain, not by HBM: with L2-resident weights they run no faster (o_proj 12.3 us cold,
+# 14.7 us hot), and the prefetch requests compete with the GEMMs' own loads.
+_L2_PREFETCH = os.environ.get("JETSPEC_L2_PREFETCH", "0") == "1"
 
 
 def _i32(n, device, fill=0):
@@ -143,8 +147,37 @@ def _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) -> int:
     return 8
 
 
+class WeightPrefetcher:
+    """Pulls the NEXT GEMM's weights into L2 on a side stream while the current kernels run.
+
+    A decode round is a chain of short dependent kernels; while attention, the norms and every GEMM's
+    prologue and epilogue run, HBM is idle.  ``ahead(w)`` is called right before a kernel is launched on
+    the main stream: the side stream waits for everything launched so far, then issues L2 prefetches for
+    ``w`` (at most ``cap`` bytes, so a prefetch never evicts what was prefetched before it and is still
+    unread).  Works eagerly and inside CUDA-graph capture (the fork/join become graph edges).
+    """
+
+    def __init__(self, device, cap_bytes: int = 72 << 20, ctas: int = 8):
+        self.side = torch.cuda.Stream(device)
+        self.cap, self.ctas = int(cap_bytes), int(ctas)
+        self.launches = 0
+
+    def ahead(self, w) -> None:
+        if not isinstance(w, torch.Tensor):
+            w = w.packed                                   # NVFP4: the codes are the bulk of the bytes
+        main = torch.cuda.current_stream()
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            X.l2_prefetch(w, self.cap, self.ctas)
+        self.launches += 1
+
+    def join(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.side)
+
+
 def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
-                   mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True, tp=None) -> int:
+                   mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True, tp=None, prefetch=None,
+                   then_prefetch=None) -> int:
     """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count."""
     Hq, Hkv, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
     scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
@@ -167,15 +200,26 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
                         X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
                         n += 1
             continue
+        pf = prefetch
         X.rmsnorm(st.x, L["ln1"], eps, out=st.h, pdl=pdl)
+        if pf is not None:
+            pf.ahead(L["o"])                   # o_proj's weights arrive while qkv, the KV scatter and attention run
         X.gemm(st.h, L["qkv"], out=st.qkv, pdl=pdl)
         attend()
+        if pf is not None:
+            pf.ahead(L["gu"])
         if tp is None:
             X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
         else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory
             tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl)
         X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
+        if pf is not None:
+            pf.ahead(L["down"])
         X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
+        if pf is not None:
+            nxt = layers[li + 1]["qkv"] if li != last else then_prefetch
+            if nxt is not None:
+                pf.ahead(nxt)
         if tp is None:
             X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
         else:
@@ -186,6 +230,8 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
                 if t == li:
                     X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
                     n += 1
+    if prefetch is not None:
+        prefetch.join()
     return n
 
 
@@ -214,6 +260,7 @@ class FastRound:
             self.vocab_local = self.cfg.vocab_size // world
             self.lm_head_w = shard_rows(m.lm_head.weight, self.tp.rank, world)
         self.freq = X.inv_freq(self.cfg.head_dim, self.cfg.rope_theta, self.device)
+        self.prefetcher = WeightPrefetcher(self.device) if _L2_PREFETCH else None
         self.graphs: dict = {}
         self.draft_cache: dict = {}
         self.launches_per_round = 0
@@ -402,10 +449,14 @@ class FastRound:
                                    pool.max_seq_len, p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["positions"]),
                                    p(r["slots"]), p(r["mask"]), p(status), int(pdl), s()), "js_tree_build")
         st = r["stack"]
+        pf = self.prefetcher
+        if pf is not None:
+            pf.ahead(self.layers[0]["qkv"])       # the first projection's weights arrive during the tree build
         X.embed(r["tokens"], self.embed_w, out=st.x, pdl=pdl)
         n += 2 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
                                 r["cu_q"], r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"],
-                                False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp)
+                                False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp,
+                                prefetch=pf, then_prefetch=self.lm_head_w)
         X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
         last = cfg.num_hidden_layers - 1
         if r["taps"] is not None:

@@ -465,6 +465,17 @@ def paged_tree_attention(q, k_pool, v_pool, slot_map, seq_rows, cu_q, past_lens,
     return out
 
 
+def l2_prefetch(t: torch.Tensor, max_bytes: Optional[int] = None, ctas: int = 8) -> None:
+    """Ask the memory system to pull the first ``max_bytes`` of ``t`` into L2 (launch on the CURRENT stream;
+    the kernel only issues ``cp.async.bulk.prefetch.L2`` requests and exits)."""
+    lib = load()
+    n = t.numel() * t.element_size()
+    if max_bytes is not None:
+        n = min(n, int(max_bytes))
+    lib.js_l2_prefetch.restype = ctypes.c_int
+    _check(lib.js_l2_prefetch(_p(t), ctypes.c_size_t(n), int(ctas), _stream()), "js_l2_prefetch")
+
+
 # ------------------------------------------------------------------ routing, sampling, compaction
 def moe_route(router_logits: torch.Tensor, top_k: int, renorm: bool, pdl: bool = False):
     """``(weights (T, k) fp32, experts (T, k) int32)``: softmax over the experts, top-k, optional renormalisation."""
