@@ -70,6 +70,8 @@ struct GemmParams {
   const uint8_t* sfw;
   const float* row_scale;
   float w_scale;
+  // EPI_ALLREDUCE: only push the partial tile and bump the flags; a finishing kernel reduces (no wait in this kernel)
+  int ar_push_only;
 };
 
 JS_DEVICE void red_release_sys_add(int* addr, int v) {
@@ -382,6 +384,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // buffer, sums them in rank order together with the residual and writes the output.  All
       // ranks add the same numbers in the same order, so the replicated result is bit-identical.
       const int fidx = (blockIdx.y * gridDim.x + blockIdx.x) * split + z;
+      if (p.ar_push_only == 2) {
+        // Low-latency push: every pair of bf16 outputs travels in ONE 8-byte store together with a flag word,
+        // so the receiver needs no fence, no counter and no extra round trip: it polls the cells themselves
+        // (the finishing kernel) and zeroes them after use.  Receive buffer: (world, m_cap, N/2) cells of 8 bytes.
+        // The chunk is staged in shared memory first so that neighbouring lanes store neighbouring bytes of one row:
+        // NVLink then sees 128-byte writes (4 lanes x 32 bytes per row) instead of one small write per lane.
+        uint8_t* stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));   // 8 KB behind the barriers
+        const int et = threadIdx.x - 64;                                   // 0..127 among the epilogue threads
+        for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
+          float v[32];
+          load_chunk(c0, v);
+          const int gc = n0 + c0;
+          epi_barrier();                                                   // previous chunk's readers are done
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint4 pk;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) o2[u] = __floats2bfloat162_rn(v[8 * t + 2 * u], v[8 * t + 2 * u + 1]);
+            *reinterpret_cast<uint4*>(stage + row * 64 + ((t ^ ((row >> 1) & 3)) << 4)) = pk;
+          }
+          epi_barrier();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int piece = et + 128 * j, prow = piece >> 2, part = piece & 3;
+            const int gr = m0 + prow, pc = gc + part * 8;
+            if (gr >= p.M || pc >= p.N) continue;
+            const uint4 d = *reinterpret_cast<const uint4*>(stage + prow * 64 + ((part ^ ((prow >> 1) & 3)) << 4));
+            const size_t cell = ((static_cast<size_t>(p.rank) * p.m_cap + gr) * p.N + pc) >> 1;
+            for (int r = 0; r < p.world; ++r) {
+              unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_recv[r]) + cell;
+              asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(d.x), "r"(1u), "r"(d.y), "r"(1u) : "memory");
+              asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(d.z), "r"(1u), "r"(d.w), "r"(1u) : "memory");
+            }
+          }
+        }
+      } else {
       for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
         float v[32];
         load_chunk(c0, v);
@@ -400,11 +439,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
-      __threadfence_system();
       epi_barrier();
       bool landed = true;
       if (threadIdx.x == 64) {
+        // one release at system scope after the CTA barrier publishes every epilogue thread's stores
+        __threadfence_system();
         for (int r = 0; r < p.world; ++r) red_release_sys_add(p.peer_flags[r] + fidx, 1);
+        if (p.ar_push_only) {
+          *reinterpret_cast<volatile int*>(tmem_slot + 1) = 0;
+        } else {
         const int* mine = p.peer_flags[p.rank] + fidx;
         landed = false;
         for (uint32_t it = 0; it < (1u << 22); ++it) {
@@ -413,6 +456,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (!landed) report(p.status, kTimeoutPeer);
         *reinterpret_cast<volatile int*>(tmem_slot + 1) = landed ? 1 : 0;
+        }
       }
       epi_barrier();
       landed = *reinterpret_cast<volatile int*>(tmem_slot + 1) != 0;
@@ -463,7 +507,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       epi_barrier();
-      if (threadIdx.x == 64 && landed) p.peer_flags[p.rank][fidx] = 0;   // ready for this buffer's next turn
+      if (threadIdx.x == 64 && landed && !p.ar_push_only) p.peer_flags[p.rank][fidx] = 0;   // ready for this buffer's next turn
+      }
     } else if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
       // 32-column chunks are dealt round-robin to the CTAs of the K-split cluster
       for (int c0 = z * 32; c0 < BN; c0 += split * 32) {
@@ -643,7 +688,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   const int recv_total = recv_bytes(split, BN, EPI == EPI_SWIGLU);
   const int data_bytes = recv_aliases_stages(S::kTiles, recv_total) ? (S::kTiles > recv_total ? S::kTiles : recv_total)
                                                                      : S::kTiles + recv_total;
-  const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/ + (EPI == EPI_ALLREDUCE ? 8192 + 64 : 0);
   if (smem_bytes > 227 * 1024) return -18;
   if (smem_bytes > configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;
@@ -717,7 +762,7 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
 extern "C" int js_gemm_bf16_allreduce(const void* A, const void* W, void* C, const void* residual, int M, int N, int K,
                                       int lda, int ldw, int ldc, int split, void* const* peer_recv,
                                       int* const* peer_flags, int rank, int world, int m_cap, int n_flags,
-                                      int* status, int pdl, cudaStream_t stream) {
+                                      int* status, int pdl, int push_only, cudaStream_t stream) {
   using namespace js;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8) || (ldc % 8) || (N % 8)) return -10;
@@ -733,6 +778,7 @@ extern "C" int js_gemm_bf16_allreduce(const void* A, const void* W, void* C, con
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), nullptr, nullptr, nullptr, status,
                nullptr, reinterpret_cast<__nv_bfloat16* const*>(peer_recv), peer_flags, rank, world, m_cap,
                nullptr, nullptr, nullptr, nullptr, nullptr};
+  p.ar_push_only = push_only;
   return split > 1 ? launch_gemm<128, EPI_ALLREDUCE, 128>(ta, tw, p, split, pdl != 0, stream)
                    : launch_gemm<128, EPI_ALLREDUCE, 96>(ta, tw, p, split, pdl != 0, stream);
 }
@@ -805,7 +851,7 @@ extern "C" int js_gemm_nvfp4_allreduce(const void* Aq, const void* sfa, const fl
                                        const void* sfw, float w_scale, void* C, const void* residual, int M, int N,
                                        int K, int lda_bytes, int ldw_bytes, int ldc, int split, void* const* peer_recv,
                                        int* const* peer_flags, int rank, int world, int m_cap, int n_flags, int* status,
-                                       int pdl, cudaStream_t stream) {
+                                       int pdl, int push_only, cudaStream_t stream) {
   using namespace js;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 256) || (lda_bytes % 16) || (ldw_bytes % 16) || (ldc % 8) || (N % 8)) return -10;
@@ -826,5 +872,6 @@ extern "C" int js_gemm_nvfp4_allreduce(const void* Aq, const void* sfa, const fl
   p.rank = rank; p.world = world; p.m_cap = m_cap;
   p.sfa = reinterpret_cast<const uint8_t*>(sfa); p.sfw = reinterpret_cast<const uint8_t*>(sfw);
   p.row_scale = row_scale; p.w_scale = w_scale;
+  p.ar_push_only = push_only;
   return launch_gemm<128, EPI_ALLREDUCE, 128, true>(ta, tw, p, split, pdl != 0, stream);
 }

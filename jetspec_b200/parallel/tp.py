@@ -91,7 +91,15 @@ class TensorParallel:
         self._X = X
         self._turn = 0
         self.ring_mod = 4
-        self.recv = [SymmetricBuffer(self.world * self.m_cap * self.n_max * 2, group) for _ in range(self.RING)]
+        # push mode (default): the GEMM only pushes its partial tiles and a finishing kernel reduces, so no GEMM CTA
+        # ever waits for a peer; JETSPEC_TP_WAIT_IN_GEMM=1 selects the single-kernel variant that waits in its epilogue
+        #   2 = low-latency cells (8 bytes = two bf16 outputs + a flag word, polled by the finishing kernel: no fence,
+        #       no counter, one NVLink crossing), 1 = bf16 tiles + one release counter per CTA, 0 = wait inside the GEMM
+        mode = os.environ.get("JETSPEC_TP_ALLREDUCE", "ll")
+        self.push_only = {"ll": 2, "flags": 1, "wait": 0}[mode]
+        if os.environ.get("JETSPEC_TP_WAIT_IN_GEMM", "0") == "1":
+            self.push_only = 0
+        self.recv = [SymmetricBuffer(self.world * self.m_cap * self.n_max * 4, group) for _ in range(self.RING)]
         self.flags = [SymmetricBuffer(self.n_flags * 4, group) for _ in range(self.RING)]
         self.am_buf = [SymmetricBuffer(self.world * 256 * 8, group) for _ in range(2)]
         self.am_flag = [SymmetricBuffer(64, group) for _ in range(2)]
@@ -116,6 +124,15 @@ class TensorParallel:
         M, K = x.shape
         N = w.shape[0]
         assert N <= self.n_max and M <= self.m_cap
+        # Every CTA of a launch waits for its peers on the other GPUs, so a launch must fit the chip in ONE wave:
+        # taller inputs go in row slabs, one launch (and one buffer of the ring) per slab.
+        n_tiles = (N + 127) // 128
+        slab = max(1, (2 * X.SM_COUNT) // n_tiles) * 128
+        if M > slab:
+            for m0 in range(0, M, slab):
+                m1 = min(M, m0 + slab)
+                self.gemm_allreduce(x[m0:m1], w, out[m0:m1], None if residual is None else residual[m0:m1], split, pdl)
+            return out
         if split is None:
             tiles = ((N + 127) // 128) * ((M + 127) // 128)
             kb = (K + 63) // 64
@@ -127,10 +144,31 @@ class TensorParallel:
         rc = lib.js_gemm_bf16_allreduce(X._p(x), X._p(w), X._p(out), X._p(residual), M, N, K, x.stride(0), w.stride(0),
                                         out.stride(0), split, X._p(self.recv[t].ptrs_dev), X._p(self.flags[t].ptrs_dev),
                                         self.rank, self.world, self.m_cap, self.n_flags,
-                                        X._p(X.status_word(x.device)), int(pdl), X._stream())
+                                        X._p(X.status_word(x.device)), int(pdl), int(self.push_only), X._stream())
         X._check(rc, f"js_gemm_bf16_allreduce(M={M},N={N},K={K},split={split})")
         self.launches += 1
+        if self.push_only:
+            self._finish(t, out, residual, M, N, split, pdl)
         return out
+
+    def _finish(self, t: int, out, residual, M: int, N: int, split: int, pdl: bool) -> None:
+        """Second kernel of the push-mode all-reduce: wait for every rank's tiles, sum in rank order, add the residual."""
+        X = self._X
+        lib = X.load()
+        if self.push_only == 2:
+            lib.js_tp_allreduce_finish_ll.restype = ctypes.c_int
+            rc = lib.js_tp_allreduce_finish_ll(ctypes.c_void_p(self.recv[t].local), X._p(residual), X._p(out), M, N,
+                                               out.stride(0), self.m_cap, self.world, X._p(X.status_word(out.device)),
+                                               int(pdl), X._stream())
+            X._check(rc, "js_tp_allreduce_finish_ll")
+            self.launches += 1
+            return
+        lib.js_tp_allreduce_finish.restype = ctypes.c_int
+        rc = lib.js_tp_allreduce_finish(ctypes.c_void_p(self.recv[t].local), ctypes.c_void_p(self.flags[t].local),
+                                        X._p(residual), X._p(out), M, N, out.stride(0), self.m_cap, self.world, split,
+                                        X._p(X.status_word(out.device)), int(pdl), X._stream())
+        X._check(rc, "js_tp_allreduce_finish")
+        self.launches += 1
 
     def gemm_allreduce_nvfp4(self, act: dict, qw, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                              split: Optional[int] = None, pdl: bool = False):
@@ -157,9 +195,12 @@ class TensorParallel:
                                          X._p(residual), M, N, K, act["packed"].stride(0), qw.packed.stride(0),
                                          out.stride(0), split, X._p(self.recv[t].ptrs_dev),
                                          X._p(self.flags[t].ptrs_dev), self.rank, self.world, self.m_cap,
-                                         self.n_flags, X._p(X.status_word(out.device)), int(pdl), X._stream())
+                                         self.n_flags, X._p(X.status_word(out.device)), int(pdl),
+                                         int(self.push_only), X._stream())
         X._check(rc, f"js_gemm_nvfp4_allreduce(M={M},N={N},K={K},split={split})")
         self.launches += 1
+        if self.push_only:
+            self._finish(t, out, residual, M, N, split, pdl)
         return out
 
     def begin_sequence(self, calls_per_replay: Optional[int] = None) -> None:
