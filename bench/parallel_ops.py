@@ -10,7 +10,7 @@ residual add.  Both run as CUDA graphs of back-to-back calls on rotating weights
 weight bytes / measured copy bandwidth and bytes crossing NVLink / 770 GB/s.
 
 ``ep``: one sparse-MoE layer on 1024 tokens, 128 experts, top-8: fused combine in the grouped down-projection epilogue
-(`ExpertParallel.moe_layer`) against local experts + NCCL all-reduce (`moe_layer_nccl`).
+(`ExpertParallel.moe_layer`) against the same grouped GEMMs + scatter + NCCL all-reduce (`moe_layer_grouped_nccl`).
 """
 import json
 import os
@@ -110,7 +110,7 @@ def bench_ep(rank: int, world: int):
         return max_ranks(a.elapsed_time(b)) * 1e3 / iters
 
     fused = timed(lambda: ep.moe_layer(x, gate, gu_l, dn_l, True))
-    twin = timed(lambda: ep.moe_layer_nccl(x, gate, wgu, wd, True), iters=3)
+    twin = timed(lambda: ep.moe_layer_grouped_nccl(x, gate, gu_l, dn_l, True))
     X.check_status("cuda")
     w_us = (E // world) * 3 * H * I * 2 / HBM_GBS / 1e3
     link_us = T * k * H * 2 * (world - 1) / world / NVLINK_GBS / 1e3      # each rank sends its experts' rows to every peer

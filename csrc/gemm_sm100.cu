@@ -353,29 +353,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // by its routing weight and stored into every rank's (token, choice) pair buffer over NVLink;
       // one release-increment per CTA and rank lets the finishing kernel know when all experts of
       // all ranks have delivered.
+      // Each 32-column chunk is staged in shared memory so that four neighbouring lanes store one row's 64
+      // contiguous bytes: NVLink sees a quarter of the write transactions of a store per lane and row.
+      uint8_t* stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
+      const int et = threadIdx.x - 64;
+      const float wgt = grow < m_end ? p.row_weight[grow] : 0.f;
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         load_chunk(c0, v);
         const int gc = n0 + c0;
-        if (grow < m_end && gc < p.N) {
-          const float wgt = p.row_weight[grow];
-          const size_t off = static_cast<size_t>(p.row_pair[grow]) * p.N + gc;
-          uint4 pk[4];
-          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(pk);
+        epi_barrier();
 #pragma unroll
-          for (int t = 0; t < 16; ++t) o2[t] = __floats2bfloat162_rn(v[2 * t] * wgt, v[2 * t + 1] * wgt);
-          for (int r = 0; r < p.world; ++r) {
-            uint4* dst = reinterpret_cast<uint4*>(p.peer_pairs[r] + off);
+        for (int t = 0; t < 4; ++t) {
+          uint4 pk;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-              if (gc + 8 * t < p.N) dst[t] = pk[t];
-          }
+          for (int u = 0; u < 4; ++u) o2[u] = __floats2bfloat162_rn(v[8 * t + 2 * u] * wgt, v[8 * t + 2 * u + 1] * wgt);
+          *reinterpret_cast<uint4*>(stage + row * 64 + ((t ^ ((row >> 1) & 3)) << 4)) = pk;
+        }
+        epi_barrier();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int piece = et + 128 * j, prow = piece >> 2, part = piece & 3;
+          const int gr = m0 + prow, pc = gc + part * 8;
+          if (gr >= m_end || pc >= p.N) continue;
+          const uint4 d = *reinterpret_cast<const uint4*>(stage + prow * 64 + ((part ^ ((prow >> 1) & 3)) << 4));
+          const size_t off = static_cast<size_t>(p.row_pair[gr]) * p.N + pc;
+          for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peer_pairs[r] + off) = d;
         }
       }
-      __threadfence_system();
       epi_barrier();
-      if (threadIdx.x == 64)
+      if (threadIdx.x == 64) {      // one release at system scope after the CTA barrier publishes every thread's stores
+        __threadfence_system();
         for (int r = 0; r < p.world; ++r) red_release_sys_add(p.peer_cnt[r], 1);
+      }
     } else if constexpr (EPI == EPI_ALLREDUCE) {
       // Row-parallel GEMM fused with the tensor-parallel all-reduce (one shot): each finished
       // 32-column chunk of this rank's partial product is stored as bf16 straight into every
@@ -688,7 +699,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   const int recv_total = recv_bytes(split, BN, EPI == EPI_SWIGLU);
   const int data_bytes = recv_aliases_stages(S::kTiles, recv_total) ? (S::kTiles > recv_total ? S::kTiles : recv_total)
                                                                      : S::kTiles + recv_total;
-  const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/ + (EPI == EPI_ALLREDUCE ? 8192 + 64 : 0);
+  const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/ + ((EPI == EPI_ALLREDUCE || EPI == EPI_EP_COMBINE) ? 8192 + 64 : 0);
   if (smem_bytes > 227 * 1024) return -18;
   if (smem_bytes > configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;

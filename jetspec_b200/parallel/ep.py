@@ -122,6 +122,35 @@ class ExpertParallel:
         self.launches += 3
         return out
 
+    def moe_layer_grouped_nccl(self, x, gate_w, gu_local, down_local, renorm, router_logits=None):
+        """Unfused twin on the SAME grouped GEMMs: local experts' outputs are stored, scattered into a dense fp32
+        partial with their routing weights, summed over the ranks by an NCCL all-reduce, then the residual is added."""
+        import torch.distributed as dist
+        X = self._X
+        lib = X.load()
+        T, H = x.shape
+        I = gu_local.shape[0] // (2 * self.n_local)
+        if router_logits is None:
+            router_logits = X.gemm(x, gate_w, epi=X.EPI_STORE_F32)
+        order, row_w, group_off, _ = route_and_sort(router_logits, self.k, renorm, self.first, self.n_local)
+        tok = torch.div(order, self.k, rounding_mode="floor")
+        xs = x.index_select(0, tok)
+        h = torch.empty(T * self.k, I, dtype=x.dtype, device=x.device)
+        y = torch.zeros(T * self.k, H, dtype=x.dtype, device=x.device)
+        st = X._p(X.status_word(x.device))
+        X._check(lib.js_gemm_bf16_grouped(X._p(xs), X._p(gu_local), X._p(h), T * self.k, 2 * I, H, xs.stride(0),
+                                          gu_local.stride(0), h.stride(0), X.EPI_SWIGLU, self.n_local, X._p(group_off),
+                                          T, None, None, None, None, 1, st, 0, X._stream()), "grouped gate/up")
+        X._check(lib.js_gemm_bf16_grouped(X._p(h), X._p(down_local), X._p(y), T * self.k, H, I, h.stride(0),
+                                          down_local.stride(0), y.stride(0), X.EPI_STORE, self.n_local, X._p(group_off),
+                                          T, None, None, None, None, 1, st, 0, X._stream()), "grouped down")
+        n_mine = group_off[-1:].long()                       # rows past the local groups belong to other ranks
+        valid = (torch.arange(T * self.k, device=x.device) < n_mine).float()[:, None]
+        part = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+        part.index_add_(0, tok, y.float() * (row_w * valid[:, 0])[:, None])
+        dist.all_reduce(part, group=self.group)
+        return (x.float() + part).to(x.dtype)
+
     def moe_layer_nccl(self, x, gate_w, w_gate_up, w_down, renorm, router_logits=None):
         """Unfused baseline twin: this rank's experts through plain PyTorch, NCCL all-reduce, residual."""
         import torch.distributed as dist

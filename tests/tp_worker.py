@@ -138,12 +138,14 @@ def ep_check(rank, world) -> bool:
     base = ep.moe_layer_nccl(x, gate, wgu, wd, True, router_logits=logits)
     err = float((out.float() - exp).abs().max() / exp.abs().max())
     err_b = float((base.float() - exp).abs().max() / exp.abs().max())
+    twin = ep.moe_layer_grouped_nccl(x, gate, gu_l, dn_l, True, router_logits=logits)
+    err_b = max(err_b, float((twin.float() - exp).abs().max() / exp.abs().max()))
     gathered = [torch.empty_like(out) for _ in range(world)]
     dist.all_gather(gathered, out)
     same = all(torch.equal(gathered[0], t) for t in gathered)
     if rank == 0:
         print(f"ep moe layer: rel err {err:.2e} (nccl twin {err_b:.2e}), replicas identical {same}", flush=True)
-    return err < 2e-2 and same
+    return err < 2e-2 and err_b < 2e-2 and same
 
 
 def nvfp4_check(tp, rank, world) -> bool:
