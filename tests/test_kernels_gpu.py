@@ -306,3 +306,25 @@ def test_kv_compact_kernel(ext):
     idx = keep.long().cuda() + past
     assert torch.equal(k[:, past:past + 6], k0[:, idx]) and torch.equal(v[:, past:past + 6], v0[:, idx])
     assert torch.equal(k[:, :past], k0[:, :past]) and torch.equal(k[:, past + 6:], k0[:, past + 6:])
+
+
+@pytest.mark.parametrize("impl", ["mma", "tc"])
+def test_corrupt_slot_map_is_reported_not_followed(ext, impl):
+    """A slot index outside the pool must never be dereferenced: the kernel substitutes slot 0, records a status
+    code the host reads after the step, and the context stays usable."""
+    Hq, Hkv, D, S, n, past = 8, 2, 128, 256, 16, 40
+    kp, vp, q = rnd(Hkv, S, D, seed=41), rnd(Hkv, S, D, seed=42), rnd(n, Hq, D, seed=43)
+    slot_map = torch.arange(S, dtype=torch.int32, device="cuda").view(1, S).clone()
+    slot_map[0, 7] = 10 ** 6                       # corrupted metadata
+    slot_map[0, 9] = -3
+    cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+    rows = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pl = torch.tensor([past], dtype=torch.int32, device="cuda")
+    out = ext.paged_tree_attention(q, kp, vp, slot_map, rows, cu, pl, None, 1 / math.sqrt(D), True, n, splits=1, impl=impl)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    with pytest.raises(RuntimeError, match="KV slot out of range"):
+        ext.check_status("cuda")
+    ext.check_status("cuda")                        # the word is cleared by the read; later kernels run normally
+    x, w = rnd(8, 256, seed=44), rnd(128, 256, seed=45)
+    assert rel_err(ext.gemm(x, w), x.float() @ w.float().t()) < BF16_TOL
