@@ -115,7 +115,8 @@ def status_word(device) -> torch.Tensor:
     dev = torch.device(device)
     key = dev.index if dev.index is not None else (torch.cuda.current_device() if dev.type == "cuda" else -1)
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):       # a normal tensor: it is cleared in place from any calling context
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
 
 
