@@ -209,6 +209,9 @@ JS_DEVICE float ld_dsmem_f32(uint32_t cluster_addr) {
 JS_DEVICE void st_dsmem_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
+JS_DEVICE void st_dsmem_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 JS_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"

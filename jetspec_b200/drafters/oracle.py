@@ -95,6 +95,12 @@ class OracleTreeDrafter(TreeDrafter):
         return (torch.tensor(rows, dtype=torch.long, device=dev),
                 torch.tensor([lp] * depth, dtype=torch.float32, device=dev))
 
+    def propose_topk_at(self, context_len: int, depth: int, width: Optional[int] = None):
+        """The same proposal as :meth:`propose_topk` from the context LENGTH alone, as Python lists (the script
+        depends only on the position; engines that stage the top-k on the host skip building tensors)."""
+        self.calls += 1
+        return self._candidates(int(context_len), depth), [self._logprobs()] * depth
+
     def propose_logits(self, context_ids, depth, target_hidden=None, **kwargs):
         self.calls += 1
         T = int(context_ids.shape[-1])

@@ -609,7 +609,13 @@ class FastRound:
         stream = torch.cuda.current_stream()
         events = []
         while len(new_ids) < sp.max_new_tokens and not done:
-            if staged:
+            if staged and oracle is not None and hasattr(oracle, "propose_topk_at"):
+                tok_l, lp_l = oracle.propose_topk_at(len(ctx_ids), D, K)      # the script needs the position only
+                stage_tok[:] = np.asarray(tok_l, dtype=np.int32)
+                stage_lp[:] = np.asarray(lp_l, dtype=np.float32)
+                stage_caps[:] = np.asarray(algo_obj.caps_from_topk(lp_l, K, prompt_info=prompt_info,
+                                                                   profile_table=profile_table), dtype=np.int32)
+            elif staged:
                 ctx_t = torch.tensor([ctx_ids], dtype=torch.long, device="cpu" if oracle is not None else eng.device)
                 if hasattr(src, "propose_topk"):
                     tok, lp = src.propose_topk(ctx_t, D, K)
