@@ -490,13 +490,10 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
           uint32_t orr[32];
           tmem_ld_32x32(tmem_o + t_lane + c * 32, orr);
           tmem_ld_wait();
-          // slot = 128 rows x 128 bytes, 16-byte pieces XOR-swizzled by the row (vector stores, conflict-free)
           const uint32_t dst = map_to_cta(smem_u32(recv_o), c % p.splits) +
-                               static_cast<uint32_t>((split * per_owner + c / p.splits) * 16384 + row * 128);
+                               static_cast<uint32_t>(((split * per_owner + c / p.splits) * 4096 + row) * 4);
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            st_dsmem_v4(dst + ((q ^ (row & 7)) << 4), __uint_as_float(orr[4 * q]), __uint_as_float(orr[4 * q + 1]),
-                        __uint_as_float(orr[4 * q + 2]), __uint_as_float(orr[4 * q + 3]));
+          for (int j = 0; j < 32; ++j) st_dsmem_f32(dst + j * (TROWS * 4), __uint_as_float(orr[j]));
         }
       }
     }
@@ -521,13 +518,9 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
         for (int j = 0; j < 32; ++j) acc[j] = 0.f;
         for (int s2 = 0; s2 < p.splits; ++s2) {
           if (wsrc[s2] == 0.f) continue;       // that split saw no visible key (its chunk was never pushed)
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(recv_o) + (s2 * per_owner + c / p.splits) * 16384 + row * 128;
+          const float* src = recv_o + (s2 * per_owner + c / p.splits) * 4096 + row;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 f = *reinterpret_cast<const float4*>(src + ((q ^ (row & 7)) << 4));
-            acc[4 * q] += f.x * wsrc[s2]; acc[4 * q + 1] += f.y * wsrc[s2];
-            acc[4 * q + 2] += f.z * wsrc[s2]; acc[4 * q + 3] += f.w * wsrc[s2];
-          }
+          for (int j = 0; j < 32; ++j) acc[j] += src[j * TROWS] * wsrc[s2];
         }
         uint4 pk[4];
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(pk);

@@ -308,14 +308,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32(t_row + ch * 32, r);
         tmem_ld_wait();
-        // slot = 128 rows x 128 bytes, 16-byte pieces XOR-swizzled by the row: eight vector stores per thread,
-        // conflict-free on both the remote write and the owner's read
         const uint32_t dst = map_to_cta(recv_addr, owner_of(ch)) +
-                             static_cast<uint32_t>((z * slots_per_src + local_of(ch)) * 16384 + row * 128);
+                             static_cast<uint32_t>((z * slots_per_src + local_of(ch)) * 16384 + row * 4);
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          st_dsmem_v4(dst + ((q ^ (row & 7)) << 4), __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                      __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        for (int j = 0; j < 32; ++j) st_dsmem_f32(dst + j * (BM * 4), __uint_as_float(r[j]));
       }
     }
     tc_fence_before();
@@ -340,12 +336,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int j = 0; j < 32; ++j) v[j] = 0.f;
         const int lo = local_of(c0 >> 5);
         for (int src = 0; src < split; ++src) {   // fixed source order: deterministic sum
-          const uint8_t* base = reinterpret_cast<const uint8_t*>(recv) + (src * slots_per_src + lo) * 16384 + row * 128;
+          const float* base = recv + (src * slots_per_src + lo) * 4096 + row;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 f = *reinterpret_cast<const float4*>(base + ((q ^ (row & 7)) << 4));
-            v[4 * q] += f.x; v[4 * q + 1] += f.y; v[4 * q + 2] += f.z; v[4 * q + 3] += f.w;
-          }
+          for (int j = 0; j < 32; ++j) v[j] += base[j * BM];
         }
       }
       if constexpr (FP4) {
