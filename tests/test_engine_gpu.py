@@ -139,3 +139,23 @@ def test_eager_kernel_batches(engine, small):
             assert len(res["token_ids"]) == 12
             agree, short = teacher_forced_agreement(small, p, res["token_ids"])
             assert agree > 0.85 and short < 0.05
+
+
+def test_moe_target_runs_on_the_kernel_path_and_is_lossless():
+    """A sparse-MoE target (router + permutation kernels, grouped tcgen05 GEMMs) through the paged engine:
+    tree decoding must reproduce the engine's own greedy tokens."""
+    from jetspec_b200 import JetSpecEngine, SamplingParams, RandomTreeDrafter
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    cfg = Qwen3Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=8,
+                      num_experts_per_tok=2, moe_intermediate_size=256, norm_topk_prob=True, model_type="qwen3_moe")
+    model = Qwen3ForCausalLM.random_init(cfg, seed=2, dtype=torch.bfloat16, device="cuda", init="stable")
+    eng = JetSpecEngine(model, device="cuda", dtype=torch.bfloat16, max_seq_len=512)
+    prompt = torch.randint(0, 4096, (1, 24), generator=torch.Generator().manual_seed(1))
+    sp = SamplingParams(0.0, 24)
+    ar = eng.generate(prompt, sp)["token_ids"]
+    out = eng.generate_tree(prompt, RandomTreeDrafter(4096, seed=3), tree_depth=4, tree_width=2, budget=8,
+                            sampling_params=sp, return_stats=True)
+    assert len(ar) == 24 and out["token_ids"] == ar
+    from jetspec_b200.ops import cuda_ext
+    cuda_ext.check_status("cuda")
