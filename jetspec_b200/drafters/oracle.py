@@ -43,6 +43,8 @@ class OracleTreeDrafter(TreeDrafter):
         self._cand_logits = [math.log(top1_mass)] + [math.log(r) for r in rest]
         self.calls = 0
         self.planned: list = []  # accepted lengths drawn so far (diagnostics)
+        self._lp_cache = None
+        self._np_cache = None
 
     def set_continuation(self, continuation: Sequence[int]) -> None:
         self.sequence = [int(t) for t in continuation]
@@ -96,10 +98,36 @@ class OracleTreeDrafter(TreeDrafter):
                 torch.tensor([lp] * depth, dtype=torch.float32, device=dev))
 
     def propose_topk_at(self, context_len: int, depth: int, width: Optional[int] = None):
-        """The same proposal as :meth:`propose_topk` from the context LENGTH alone, as Python lists (the script
-        depends only on the position; engines that stage the top-k on the host skip building tensors)."""
+        """The same proposal as :meth:`propose_topk` from the context LENGTH alone (the script depends only on the
+        position): ``(tokens (depth, K) int32 array, log-probs (depth, K) list)``.  Engines that stage the top-k on
+        the host use this to skip building tensors every round."""
+        import numpy as np
         self.calls += 1
-        return self._candidates(int(context_len), depth), [self._logprobs()] * depth
+        T, V, K = int(context_len), self.vocab_size, self.tree_width
+        a = self.planned_accept(T, depth)
+        self.planned.append(a)
+        c = self._np_cache
+        if c is None or c[0] != (depth, K) or c[1] is not self.sequence:
+            seq = np.full(len(self.sequence) + depth, -1, dtype=np.int64)
+            seq[:len(self.sequence)] = self.sequence
+            c = self._np_cache = ((depth, K), self.sequence, seq, np.arange(depth, dtype=np.int64) * 40_503 + 17,
+                                  np.arange(K + 1, dtype=np.int64)[None, :], np.arange(K, dtype=np.int64)[None, :],
+                                  np.arange(depth, dtype=np.int64)[:, None])
+        _, _, seq, d_term, kk1, j, rowi = c
+        truth = seq[T:T + depth] if T + depth <= len(seq) else np.full(depth, -1, dtype=np.int64)
+        start = (T * 2_654_435_761 + d_term) % V
+        # K + 1 consecutive fillers per depth, the true token struck out, then the first K (or K - 1 behind the truth)
+        cand = (start[:, None] + kk1) % V
+        same = cand == truth[:, None]
+        hit = np.where(same.any(axis=1), same.argmax(axis=1), K + 1)          # where the truth sits among the fillers
+        fill = cand[rowi, j + (j >= hit[:, None])]                            # fillers with the truth skipped
+        rows = fill
+        if a > 0:
+            lead = (rowi[:, 0] < a) & (truth >= 0)
+            rows = np.where(lead[:, None], np.concatenate([truth[:, None], fill[:, :K - 1]], axis=1), fill)
+        if self._lp_cache is None:
+            self._lp_cache = self._logprobs()
+        return rows.astype(np.int32), [self._lp_cache] * depth
 
     def propose_logits(self, context_ids, depth, target_hidden=None, **kwargs):
         self.calls += 1
