@@ -3,8 +3,8 @@
 // One process drives one GPU.  A buffer allocated here with cudaMalloc is exported as a CUDA
 // IPC handle, the handles are exchanged through the host-side process group, and every rank
 // maps every peer's buffer into its own address space.  Kernels then read and write peer
-// memory with ordinary loads and stores over NVLink (no TMA multicast, no library kernel is
-// ever handed a peer pointer).
+// memory with ordinary loads and stores over NVLink (no bulk-tensor copy ever reads a peer's
+// memory, and no library kernel is ever handed a peer pointer).
 #include "common.cuh"
 
 #include <string.h>
