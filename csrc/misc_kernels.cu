@@ -196,78 +196,104 @@ __global__ void argmax_merge_kernel(const float* part_val, const int* part_idx, 
 }
 
 // Merge per-tile top-8 and (max, sum-exp) partials into per-row top-K tokens and full-vocabulary
-// log-probabilities.  One CTA (128 threads) per row.
-__global__ void topk_merge_kernel(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles,
-                                  int M, int K, int* out_tok, float* out_lp) {
+// log-probabilities.
+JS_DEVICE bool cand_better(float v1, int i1, float v2, int i2) { return v1 > v2 || (v1 == v2 && i1 < i2); }
+
+// One block per row.  Each thread folds the sorted 8-entry lists of its tiles into a private sorted
+// top-8 (registers, one pass over global memory, coalesced 32-byte reads), then K block-wide argmax
+// rounds over the threads' list heads pick the row's top-K.  Vocabulary tiles are disjoint, so a token
+// id appears in one list only and the winner of a round is identified by its id.
+__global__ void __launch_bounds__(256)
+topk_merge_kernel(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles,
+                  int M, int K, int* out_tok, float* out_lp) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
   if (row >= M) return;
-  __shared__ float s_m[128], s_s[128];
-  __shared__ float s_v[128];
-  __shared__ int s_i[128];
-  const int tid = threadIdx.x;
-  // log-sum-exp over tiles
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = 8;
+  __shared__ float s_m[kWarps], s_s[kWarps];
+  __shared__ float s_v[2][kWarps];
+  __shared__ int s_i[2][kWarps];
+  float lv[8];
+  int li[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { lv[e] = -INFINITY; li[e] = 0x7fffffff; }
   float mx = -INFINITY, se = 0.f;
-  for (int i = tid; i < n_tiles; i += blockDim.x) {
-    const float m = part_lse[(static_cast<size_t>(row) * n_tiles + i) * 2];
-    const float s = part_lse[(static_cast<size_t>(row) * n_tiles + i) * 2 + 1];
-    if (m == -INFINITY) continue;
-    if (m > mx) { se = se * __expf(mx - m) + s; mx = m; } else { se += s * __expf(m - mx); }
+  for (int t = tid; t < n_tiles; t += blockDim.x) {
+    const size_t o = static_cast<size_t>(row) * n_tiles + t;
+    const float2 ms = *reinterpret_cast<const float2*>(part_lse + o * 2);
+    if (ms.x != -INFINITY) {
+      if (ms.x > mx) { se = se * __expf(mx - ms.x) + ms.y; mx = ms.x; } else { se += ms.y * __expf(ms.x - mx); }
+    }
+    const float4 va = *reinterpret_cast<const float4*>(part_val + o * 8);
+    const float4 vb = *reinterpret_cast<const float4*>(part_val + o * 8 + 4);
+    const int4 ia = *reinterpret_cast<const int4*>(part_idx + o * 8);
+    const int4 ib = *reinterpret_cast<const int4*>(part_idx + o * 8 + 4);
+    const float tv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    const int ti[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float v = tv[e];
+      int ix = ti[e];
+      if (v < lv[7]) break;                                // the tile's list is sorted: nothing further can enter
+      if (!cand_better(v, ix, lv[7], li[7])) continue;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {                        // insert, pushing the displaced entry down
+        if (cand_better(v, ix, lv[q], li[q])) {
+          const float fv = lv[q];
+          const int fi = li[q];
+          lv[q] = v; li[q] = ix;
+          v = fv; ix = fi;
+        }
+      }
+    }
   }
-  s_m[tid] = mx;
-  s_s[tid] = se;
+  // log-sum-exp of the row: warp shuffle, then the 8 warp results
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, mx, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, se, o);
+    const float m = fmaxf(mx, m2);
+    if (m != -INFINITY) { se = se * __expf(mx - m) + s2 * __expf(m2 - m); mx = m; }
+  }
+  if (lane == 0) { s_m[warp] = mx; s_s[warp] = se; }
   __syncthreads();
-  for (int o = blockDim.x / 2; o > 0; o >>= 1) {
-    if (tid < o) {
-      const float m1 = s_m[tid], m2 = s_m[tid + o];
-      const float m = fmaxf(m1, m2);
-      if (m != -INFINITY) {
-        s_s[tid] = s_s[tid] * __expf(m1 - m) + s_s[tid + o] * __expf(m2 - m);
-        s_m[tid] = m;
-      }
-    }
-    __syncthreads();
+  float gm = -INFINITY, gs = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const float m2 = s_m[w], s2 = s_s[w];
+    const float m = fmaxf(gm, m2);
+    if (m != -INFINITY) { gs = gs * __expf(gm - m) + s2 * __expf(m2 - m); gm = m; }
   }
-  const float lse = s_m[0] + logf(s_s[0]);
-  // K rounds of global argmax over the tiles' sorted candidate lists; a candidate emitted in
-  // an earlier round is recognised by its token id and skipped.
-  __shared__ int taken[8];
-  for (int k = 0; k < K; ++k) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = tid; i < n_tiles; i += blockDim.x) {
-      const size_t o = (static_cast<size_t>(row) * n_tiles + i) * 8;
-      for (int e = 0; e < 8; ++e) {
-        const float v = part_val[o + e];
-        const int ix = part_idx[o + e];
-        if (v < bv) break;   // lists are sorted descending
-        bool used = false;
-        for (int q = 0; q < k; ++q) used |= (taken[q] == ix);
-        if (used) continue;
-        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
-        break;               // first unused entry of a sorted list is that list's best
-      }
+  const float lse = gm + logf(gs);
+  for (int k = 0; k < K && k < 8; ++k) {
+    float bv = lv[0];
+    int bi = li[0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (cand_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    s_v[tid] = bv;
-    s_i[tid] = bi;
+    const int buf = k & 1;
+    if (lane == 0) { s_v[buf][warp] = bv; s_i[buf][warp] = bi; }
     __syncthreads();
-    for (int o = blockDim.x / 2; o > 0; o >>= 1) {
-      if (tid < o) {
-        const float ov = s_v[tid + o];
-        const int oi = s_i[tid + o];
-        if (ov > s_v[tid] || (ov == s_v[tid] && oi < s_i[tid])) { s_v[tid] = ov; s_i[tid] = oi; }
-      }
-      __syncthreads();
+    bv = s_v[buf][0];
+    bi = s_i[buf][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w)
+      if (cand_better(s_v[buf][w], s_i[buf][w], bv, bi)) { bv = s_v[buf][w]; bi = s_i[buf][w]; }
+    if (li[0] == bi && lv[0] == bv && bi != 0x7fffffff) {     // this thread's head won: pop it
+#pragma unroll
+      for (int q = 0; q < 7; ++q) { lv[q] = lv[q + 1]; li[q] = li[q + 1]; }
+      lv[7] = -INFINITY; li[7] = 0x7fffffff;
     }
     if (tid == 0) {
-      taken[k] = s_i[0];
-      out_tok[row * K + k] = s_i[0];
-      out_lp[row * K + k] = s_v[0] - lse;
+      out_tok[row * K + k] = bi;
+      out_lp[row * K + k] = bv - lse;
     }
-    __syncthreads();
   }
-
 }
 
 static cudaLaunchAttribute g_pdl_attr;
@@ -343,5 +369,5 @@ extern "C" int js_topk_merge(const float* part_val, const int* part_idx, const f
                              int K, int* out_tok, float* out_lp, int pdl, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (K < 1 || K > 8) return -10;
-  JS_LAUNCH(js::topk_merge_kernel, dim3(M), dim3(128), part_val, part_idx, part_lse, n_tiles, M, K, out_tok, out_lp);
+  JS_LAUNCH(js::topk_merge_kernel, dim3(M), dim3(256), part_val, part_idx, part_lse, n_tiles, M, K, out_tok, out_lp);
 }

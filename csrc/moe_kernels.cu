@@ -118,6 +118,50 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
   }
 }
 
+// inverse of the sort: inv[pair] = row of that pair in the expert-sorted order
+__global__ void moe_invert_kernel(const int* __restrict__ order, int P, int* __restrict__ inv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < P) {
+    const int p = order[i];
+    if (p >= 0 && p < P) inv[p] = i;
+  }
+}
+
+// out[t] = sum_j row_weight[r] * ys[r], r = inv[t*k + j], summed in choice order j = 0..k-1 in fp32
+// (no atomics: a token's result does not depend on how the other tokens were routed or scheduled)
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, int ld, const int* __restrict__ inv,
+                   const float* __restrict__ row_weight, int T, int k, int H, __nv_bfloat16* __restrict__ out, int ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int r = inv[t * k + j];
+      const float w = row_weight[r];
+      const uint4 raw = *reinterpret_cast<const uint4*>(ys + static_cast<size_t>(r) * ld + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ldo + c) = o;
+  }
+}
+
 }  // namespace js
 
 // logits (T, E) fp32 -> wts (T, k) fp32, idx (T, k) int32.  E <= 256, k <= 32.
@@ -160,4 +204,28 @@ extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int f
   c.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&c, js::moe_sort_kernel, idx, wts, P, E, first, n_local, order, row_weight, group_off,
                             counts_all) == cudaSuccess ? 0 : -4;
+}
+
+// ys (T*k, H) bf16 in expert-sorted row order -> out (T, H) bf16: each token's k expert outputs weighted and
+// summed in choice order.  `inv` is a (T*k) int32 scratch.  H a multiple of 8, rows 16-byte aligned.
+extern "C" int js_moe_combine(const void* ys, int ld, const int* order, const float* row_weight, int T, int k, int H,
+                              int* inv, void* out, int ldo, int pdl, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (k < 1 || H % 8 || ld % 8 || ldo % 8) return -10;
+  const int P = T * k;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3((P + 255) / 256);
+  c.blockDim = dim3(256);
+  c.stream = stream;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  if (cudaLaunchKernelEx(&c, js::moe_invert_kernel, order, P, inv) != cudaSuccess) return -4;
+  c.gridDim = dim3(T);
+  c.blockDim = dim3(128);
+  return cudaLaunchKernelEx(&c, js::moe_combine_kernel, static_cast<const __nv_bfloat16*>(ys), ld,
+                            static_cast<const int*>(inv), row_weight, T, k, H, static_cast<__nv_bfloat16*>(out),
+                            ldo) == cudaSuccess ? 0 : -4;
 }

@@ -22,6 +22,8 @@ namespace js {
 
 constexpr int kMaxNodes = 256;
 constexpr int kMaxWords = kMaxNodes / 32;
+constexpr int kMaxCand = 512;       // depth x width entries of the candidate table staged in shared memory
+constexpr int kMaxCapDepth = 64;
 
 // sequence state (int32 words) shared by the round's kernels
 enum : int { ST_PAST = 0, ST_CTX = 1, ST_NEW = 2, ST_DONE = 3, ST_GEN = 4, ST_NNODES = 5, ST_ROUNDS = 6 };
@@ -47,17 +49,30 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
   __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes];
   __shared__ int s_bits[kMaxNodes][kMaxWords];
   __shared__ int s_n;
+  // the candidate table, staged once by the whole block: the serial expansion below then never waits on
+  // global memory (one dependent global load per pushed node was most of this kernel's time)
+  __shared__ float c_lp[kMaxCand];
+  __shared__ int c_tok[kMaxCand], c_cap[kMaxCapDepth];
   const int tid = threadIdx.x;
   const int past = state[ST_PAST];
   if (budget > NB) budget = NB;
+  const bool staged = D * K <= kMaxCand && D <= kMaxCapDepth;
+  if (staged) {
+    for (int i = tid; i < D * K; i += blockDim.x) {
+      c_lp[i] = topk_lp[i];
+      c_tok[i] = topk_tok[i];
+    }
+    for (int i = tid; i < D; i += blockDim.x) c_cap[i] = (caps != nullptr) ? caps[i] : K;
+  }
+  __syncthreads();
+  const float* lp_tab = staged ? c_lp : topk_lp;
+  const int* tok_tab = staged ? c_tok : topk_tok;
 
   if (tid == 0) {
     int n = 1, hs = 0, order = 0;
     s_tok[0] = committed[past];
     s_par[0] = -1;
     s_dep[0] = 0;
-    for (int w = 0; w < W; ++w) s_bits[0][w] = 0;
-    s_bits[0][0] = 1;
     heap[hs++] = HeapItem{0.0, 0, 0};
     while (hs > 0 && n < budget) {
       // pop min
@@ -76,16 +91,14 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
       const int node = top.node;
       const int d = s_dep[node];
       if (d >= D) continue;
-      int take = (caps != nullptr) ? caps[d] : K;
+      int take = staged ? c_cap[d] : ((caps != nullptr) ? caps[d] : K);
       if (take > K) take = K;
       if (take > budget - n) take = budget - n;
       for (int j = 0; j < take; ++j) {
-        const double cum = -top.key + static_cast<double>(topk_lp[d * K + j]);
-        s_tok[n] = topk_tok[d * K + j];
+        const double cum = -top.key + static_cast<double>(lp_tab[d * K + j]);
+        s_tok[n] = tok_tab[d * K + j];
         s_par[n] = node;
         s_dep[n] = d + 1;
-        for (int w = 0; w < W; ++w) s_bits[n][w] = s_bits[node][w];
-        s_bits[n][n >> 5] |= (1 << (n & 31));
         // push
         HeapItem it{-cum, ++order, n};
         int h = hs++;
@@ -101,6 +114,23 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
     }
     s_n = n;
     state[ST_NNODES] = n;
+  }
+  __syncthreads();
+  // ancestor bits, one node per thread: walk the parent chain (parents precede children, depth <= D)
+  for (int i = tid; i < s_n; i += blockDim.x) {
+    int bits[kMaxWords];
+#pragma unroll
+    for (int w = 0; w < kMaxWords; ++w) bits[w] = 0;
+    int c = i, steps = 0;
+    while (c >= 0 && steps <= kMaxNodes) {
+#pragma unroll
+      for (int w = 0; w < kMaxWords; ++w)
+        if (w == (c >> 5)) bits[w] |= (1 << (c & 31));
+      c = s_par[c];
+      ++steps;
+    }
+#pragma unroll
+    for (int w = 0; w < kMaxWords; ++w) s_bits[i][w] = bits[w];
   }
   __syncthreads();
   const int n = s_n;

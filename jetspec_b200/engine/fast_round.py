@@ -68,19 +68,22 @@ def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
             out.append(d)
         return _finish_layer_weights(out)
     for layer in layers:
-        if not isinstance(layer.mlp, MLP):
-            raise NotImplementedError("the graph path covers dense MLP layers")
         a = layer.self_attn
         if a.q_proj.bias is not None:
             raise NotImplementedError("the graph path covers bias-free attention projections")
-        out.append({
+        d = {
             "ln1": layer.input_layernorm.weight, "ln2": layer.post_attention_layernorm.weight,
             "qkv": stack_rows([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight]),
             "kv": stack_rows([a.k_proj.weight, a.v_proj.weight]),
             "qn": a.q_norm.weight, "kn": a.k_norm.weight, "o": a.o_proj.weight,
-            "gu": X.interleave_gate_up(layer.mlp.gate_proj.weight, layer.mlp.up_proj.weight, 128),
-            "down": layer.mlp.down_proj.weight,
-        })
+        }
+        if isinstance(layer.mlp, MLP):
+            d["gu"] = X.interleave_gate_up(layer.mlp.gate_proj.weight, layer.mlp.up_proj.weight, 128)
+            d["down"] = layer.mlp.down_proj.weight
+        else:   # sparse MoE: router + permutation kernels and two grouped GEMMs, all static-shape (no host read)
+            m = layer.mlp
+            d["moe"] = (m.gate.weight, m.w_gate_up, m.w_down, int(m.top_k), bool(m.norm_topk_prob))
+        out.append(d)
     return _finish_layer_weights(out)
 
 
@@ -206,13 +209,23 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             pf.ahead(L["o"])                   # o_proj's weights arrive while qkv, the KV scatter and attention run
         X.gemm(st.h, L["qkv"], out=st.qkv, pdl=pdl)
         attend()
-        if pf is not None:
+        if pf is not None and "gu" in L:
             pf.ahead(L["gu"])
         if tp is None:
             X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
         else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory
             tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl)
         X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
+        if "moe" in L:
+            gate_w, w_gu, w_dn, top_k, renorm = L["moe"]
+            st.x.add_(X.moe_forward(st.h, gate_w, w_gu, w_dn, top_k, renorm))
+            n += 6 + merge_launch + 7          # + router GEMM, route, sort, two grouped GEMMs, invert and combine
+            if taps is not None and li != last:
+                for j, t in enumerate(tap_ids):
+                    if t == li:
+                        X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
+                        n += 1
+            continue
         if pf is not None:
             pf.ahead(L["down"])
         X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
@@ -271,7 +284,7 @@ class FastRound:
     # ------------------------------------------------------------------ support matrix
     def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget) -> bool:
         cfg = self.cfg
-        if cfg.head_dim != 128 or cfg.is_moe or budget > 256 or tree_width > 8 or block_size - 1 > 48:
+        if cfg.head_dim != 128 or budget > 256 or tree_width > 8 or block_size - 1 > 48:
             return False
         return hasattr(algo_obj, "caps_from_topk")
 
@@ -671,7 +684,7 @@ class FastRound:
     def generate_ar(self, sid, ids, sp: SamplingParams):
         """Autoregressive decode = rounds with a one-node tree (budget 1, no drafter)."""
         eng = self.eng
-        if sp.temperature > 0.0 or self.cfg.head_dim != 128 or self.cfg.is_moe:
+        if sp.temperature > 0.0 or self.cfg.head_dim != 128:
             logits, _ = eng._prefill(sid, ids[0], reserve=sp.max_new_tokens + 1)
             out = [int(sample(logits[-1], sp.temperature))]
             while len(out) < sp.max_new_tokens and out[-1] not in eng.eos_token_ids:

@@ -557,7 +557,11 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
     gu, dn = _moe_cache[key]
     if router_logits is None:
         router_logits = gemm(x, gate_w, epi=EPI_STORE_F32) if gemm_supported(T, E, H) else torch.nn.functional.linear(x, gate_w)
-    order, row_w, group_off, _ = route_and_sort(router_logits, top_k, renorm, 0, E)
+    on_device = E <= 256 and T * top_k <= 16384
+    if on_device:    # router + permutation kernels: int32 order, no host synchronisation, static shapes
+        order, row_w, group_off, _ = moe_route_sort(router_logits.float(), top_k, renorm, 0, E)
+    else:
+        order, row_w, group_off, _ = route_and_sort(router_logits, top_k, renorm, 0, E)
     tok = torch.div(order, top_k, rounding_mode="floor")
     xs = x.index_select(0, tok)
     h = torch.empty(T * top_k, I, dtype=x.dtype, device=x.device)
@@ -569,6 +573,14 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
     _check(lib.js_gemm_bf16_grouped(_p(h), _p(dn), _p(ys), T * top_k, H, I, h.stride(0), dn.stride(0), ys.stride(0),
                                     EPI_STORE, E, _p(group_off), T, None, None, None, None, 1, st, 0, _stream()),
            "grouped down")
+    if on_device and x.dtype == torch.bfloat16:
+        # weighted sum of each token's expert outputs in choice order (fixed order, no atomics)
+        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        inv = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
+        lib.js_moe_combine.restype = ctypes.c_int
+        _check(lib.js_moe_combine(_p(ys), ys.stride(0), _p(order), _p(row_w), T, top_k, H, _p(inv), _p(out),
+                                  out.stride(0), 0, _stream()), "js_moe_combine")
+        return out
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    out.index_add_(0, tok, ys.float() * row_w[:, None])
+    out.index_add_(0, tok.long(), ys.float() * row_w[:, None])
     return out.to(x.dtype)
