@@ -133,7 +133,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int kStages = S::kStages;
   static_assert(!FP4 || BN == 128, "the NVFP4 path is built for 128-column tiles");
   // FP4: accumulator in columns [0,128), block scales of stage s in [128 + 32 s, 128 + 32 s + 32)
-  constexpr uint32_t kTmemCols = FP4 ? 256 : (BN < 32 ? 32 : BN);   // power of two
+  constexpr uint32_t kTmemCols = FP4 ? 256 : (BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256);   // power of two
   constexpr int kXStep = FP4 ? 128 : BK;              // TMA x advance per k-block (bytes resp. bf16 elements)
   constexpr int kKPerBlock = FP4 ? 256 : BK;          // K elements per pipeline stage
 
@@ -731,7 +731,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
 }  // namespace js
 
 // C = A[M,K] * W[N,K]^T.  epi: 0 store(+residual) 1 swiglu 2 argmax partials 3 top-8 + lse partials 4 fp32 store.
-// bn in {64,128,256}; split = K-split cluster size (1..4; store/swiglu only); deep selects the pipeline's
+// bn in {64,128,256} (SwiGLU also 192: 128 tiles of a 24576-wide gate/up fill one wave); split = K-split cluster size (1..4; store/swiglu only); deep selects the pipeline's
 // shared-memory budget: 0 = 96 KB (two CTAs per SM), 2 = 128 KB, 1 = 192 KB (one CTA per SM).
 // Returns 0 or a negative code.
 extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* residual, int M, int N, int K, int lda,
@@ -759,7 +759,7 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
                        : launch_gemm<BN_, EPI_, 96>(ta, tw, p, split, pdl != 0, stream);
   JS_CASE(64, EPI_STORE) JS_CASE(128, EPI_STORE) JS_CASE(256, EPI_STORE)
   JS_CASE(128, EPI_STORE_F32)
-  JS_CASE(128, EPI_SWIGLU) JS_CASE(256, EPI_SWIGLU)
+  JS_CASE(128, EPI_SWIGLU) JS_CASE(192, EPI_SWIGLU) JS_CASE(256, EPI_SWIGLU)
   JS_CASE(128, EPI_ARGMAX)
   JS_CASE(128, EPI_TOPK)
 #undef JS_CASE

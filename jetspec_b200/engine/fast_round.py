@@ -78,7 +78,9 @@ def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
             "qn": a.q_norm.weight, "kn": a.k_norm.weight, "o": a.o_proj.weight,
         }
         if isinstance(layer.mlp, MLP):
-            d["gu"] = X.interleave_gate_up(layer.mlp.gate_proj.weight, layer.mlp.up_proj.weight, 128)
+            g = layer.mlp.gate_proj.weight
+            d["gu_bn"] = X.gu_tile(g.shape[0]) if isinstance(g, torch.Tensor) else 128   # the NVFP4 kernel has 128-column tiles
+            d["gu"] = X.interleave_gate_up(g, layer.mlp.up_proj.weight, d["gu_bn"])
             d["down"] = layer.mlp.down_proj.weight
         else:   # sparse MoE: router + permutation kernels and two grouped GEMMs, all static-shape (no host read)
             m = layer.mlp
@@ -228,7 +230,7 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             continue
         if pf is not None:
             pf.ahead(L["down"])
-        X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, pdl=pdl)
+        X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, bn=L.get("gu_bn"), pdl=pdl)
         if pf is not None:
             nxt = layers[li + 1]["qkv"] if li != last else then_prefetch
             if nxt is not None:

@@ -159,7 +159,17 @@ def gemm_supported(M: int, N: int, K: int) -> bool:
     return K % 8 == 0 and N % 8 == 0 and K >= 64
 
 
-def pick_gemm_config(M: int, N: int, K: int, epi: int):
+def gu_tile(intermediate: int) -> int:
+    """Tile width of the fused gate/up GEMM (the weight is interleaved at this granularity): 128, or the value of
+    ``JETSPEC_GU_TILE`` (128, 192 or 256).  192 columns turn Qwen3-8B's 192 tiles of 128 columns (two CTAs on 44 of
+    the 148 SMs) into one even wave of 128 CTAs, but measured slower in the decode round (5.77 against 5.61 ms):
+    with one CTA per SM nothing streams while a tile's SwiGLU epilogue runs, whereas two shallow CTAs per SM
+    overlap one's epilogue with the other's loads."""
+    env = os.environ.get("JETSPEC_GU_TILE")
+    return int(env) if env else 128
+
+
+def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None):
     """``(bn, split, deep)``: tile width, K-split cluster size, pipeline variant.
 
     Decode shapes are weight-streaming bound, so the goal is enough CTAs to cover the
@@ -169,7 +179,7 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int):
     key = (M, N, K, epi)
     if key in GEMM_TUNING:
         return GEMM_TUNING[key]
-    bn = 128
+    bn = bn or 128
     m_tiles = (M + 127) // 128
     tiles = m_tiles * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
@@ -199,7 +209,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1
-    cb, cs, cd = pick_gemm_config(M, N, K, epi)
+    cb, cs, cd = pick_gemm_config(M, N, K, epi, bn)
     bn = bn or cb
     split = split or cs
     deep = cd if deep is None else deep

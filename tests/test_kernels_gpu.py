@@ -68,6 +68,19 @@ def test_gemm_swiglu(ext, split, bn):
     assert rel_err(out, ref) < BF16_TOL
 
 
+@pytest.mark.parametrize("split", [1, 2])
+def test_gemm_swiglu_192_column_tiles(ext, split):
+    """The 192-column tile (96 gate + 96 up columns): one even wave for a 24576-wide gate/up (opt-in, measured slower)."""
+    M, H, I = 128, 512, 1152
+    x, g, u = rnd(M, H, seed=8), rnd(I, H, scale=0.05, seed=9), rnd(I, H, scale=0.05, seed=10)
+    w = ext.interleave_gate_up(g, u, 192)
+    ref = torch.nn.functional.silu(x.float() @ g.float().t()) * (x.float() @ u.float().t())
+    for deep in (0, 1):
+        out = ext.gemm(x, w, epi=ext.EPI_SWIGLU, bn=192, split=split, deep=deep)
+        torch.cuda.synchronize()
+        assert rel_err(out, ref) < BF16_TOL
+
+
 def test_lm_head_argmax(ext):
     M, V, H = 128, 5000, 512       # V not a multiple of the tile width
     h, w = rnd(M, H, seed=11), rnd(V, H, scale=0.05, seed=12)
