@@ -72,7 +72,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 __global__ void __launch_bounds__(kSortThreads)
 moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int P, int E, int first, int n_local,
                 int* __restrict__ order, float* __restrict__ row_weight, int* __restrict__ group_off,
-                int* __restrict__ counts_all) {
+                int* __restrict__ counts_all, int k, int* __restrict__ token_of_row) {
   extern __shared__ int sh[];
   int* key = sh;                       // P
   int* cnt = key + P;                  // n_local + 1
@@ -92,10 +92,22 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
     if (e >= 0 && e < E) atomicAdd(&call[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {   // exclusive scan of the n_local + 1 counts by one warp, 32 entries per step
+    const int ln = threadIdx.x;
     int run = 0;
-    for (int i = 0; i <= n_local; ++i) { off[i] = run; run += cnt[i]; }
-    off[n_local + 1] = run;
+    for (int i0 = 0; i0 <= n_local; i0 += 32) {
+      const int i = i0 + ln;
+      const int c = i <= n_local ? cnt[i] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (ln >= o) inc += v;
+      }
+      if (i <= n_local) off[i] = run + inc - c;
+      run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (ln == 0) off[n_local + 1] = run;
   }
   __syncthreads();
   for (int i = threadIdx.x; i <= n_local; i += blockDim.x) group_off[i] = off[i];
@@ -112,6 +124,7 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
         const int pos = base + __popc(m & ((1u << lane) - 1u));
         order[pos] = p;
         row_weight[pos] = wts[p];
+        if (token_of_row != nullptr) token_of_row[pos] = p / k;
       }
       base += __popc(m);
     }
@@ -181,10 +194,13 @@ extern "C" int js_moe_route(const float* logits, int T, int E, int k, int renorm
   return cudaLaunchKernelEx(&c, js::moe_route_kernel, logits, T, E, k, renorm, wts, idx) == cudaSuccess ? 0 : -4;
 }
 
-// idx / wts (P = T*k) -> order (P), row_weight (P), group_off (n_local + 1), counts_all (E).
+// idx / wts (P = T*k) -> order (P), row_weight (P), group_off (n_local + 1), counts_all (E) and, when
+// token_of_row is given, the source token order[r] / k of every sorted row (the gather index of the dispatch).
 extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int first, int n_local, int* order,
-                           float* row_weight, int* group_off, int* counts_all, int pdl, cudaStream_t stream) {
+                           float* row_weight, int* group_off, int* counts_all, int k, int* token_of_row, int pdl,
+                           cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (k < 1) return -10;
   if (P > js::kSortMaxPairs || n_local < 1 || E < 1) return -10;
   const int smem = (P + 2 * n_local + 3 + E) * 4;
   static int configured = 0;
@@ -203,7 +219,7 @@ extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int f
   c.attrs = &a;
   c.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&c, js::moe_sort_kernel, idx, wts, P, E, first, n_local, order, row_weight, group_off,
-                            counts_all) == cudaSuccess ? 0 : -4;
+                            counts_all, k, token_of_row) == cudaSuccess ? 0 : -4;
 }
 
 // ys (T*k, H) bf16 in expert-sorted row order -> out (T, H) bf16: each token's k expert outputs weighted and

@@ -3,7 +3,7 @@
 // host read at the end.
 //
 // tree_build: best-first expansion under a node budget, bit-identical to the host builder
-// (max-heap on cumulative log-probability held in double, ties broken by insertion order;
+// (largest cumulative log-probability first, held in double, ties broken by insertion order;
 // per-depth fan-out caps; the budget counts the root).  Also emits what the verify forward
 // needs: rotary positions (past + depth), KV slots of the tree window, packed ancestor bits,
 // and pad rows up to the graph's bucket size (token 0, last real position, self-only mask).
@@ -28,16 +28,6 @@ constexpr int kMaxCapDepth = 64;
 // sequence state (int32 words) shared by the round's kernels
 enum : int { ST_PAST = 0, ST_CTX = 1, ST_NEW = 2, ST_DONE = 3, ST_GEN = 4, ST_NNODES = 5, ST_ROUNDS = 6 };
 
-struct HeapItem {
-  double key;   // negated cumulative log-probability
-  int order;
-  int node;
-};
-
-JS_DEVICE bool heap_less(const HeapItem& a, const HeapItem& b) {
-  return a.key < b.key || (a.key == b.key && a.order < b.order);
-}
-
 __global__ void __launch_bounds__(256, 1)
 tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget, int NB, int W,
                   const int* committed, int* state, const int* slot_map, const int* seq_row, int max_len,
@@ -45,7 +35,6 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
   pdl_launch_dependents();
   pdl_wait();
   const int* slot_row = slot_map + static_cast<size_t>(*seq_row) * max_len;
-  __shared__ HeapItem heap[kMaxNodes + 1];
   __shared__ int s_tok[kMaxNodes], s_par[kMaxNodes], s_dep[kMaxNodes];
   __shared__ int s_bits[kMaxNodes][kMaxWords];
   __shared__ int s_n;
@@ -68,50 +57,62 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
   const float* lp_tab = staged ? c_lp : topk_lp;
   const int* tok_tab = staged ? c_tok : topk_tok;
 
+  // Best-first expansion without a heap.  Nodes are numbered in push order, so "insertion order" IS the node index
+  // and the heap's pop (smallest (key, order)) is an argmin over the nodes that were pushed and not yet popped.
+  // Thread i owns node i: its key lives in a register; one block-wide argmin (shuffles + one barrier) per pop
+  // replaces the serial sift-down, and the children of the popped node are written by `take` threads at once.
+  __shared__ double r_key[2][8];
+  __shared__ int r_idx[2][8];
+  const int lane = tid & 31, warp = tid >> 5;
+  double my_key = 0.0;            // negated cumulative log-probability of node `tid`
+  bool alive = (tid == 0);
+  int n = 1, max_dep = 0;      // uniform across the block
   if (tid == 0) {
-    int n = 1, hs = 0, order = 0;
     s_tok[0] = committed[past];
     s_par[0] = -1;
     s_dep[0] = 0;
-    heap[hs++] = HeapItem{0.0, 0, 0};
-    while (hs > 0 && n < budget) {
-      // pop min
-      const HeapItem top = heap[0];
-      const HeapItem last = heap[--hs];
-      int i = 0;
-      while (true) {
-        int c = 2 * i + 1;
-        if (c >= hs) break;
-        if (c + 1 < hs && heap_less(heap[c + 1], heap[c])) ++c;
-        if (!heap_less(heap[c], last)) break;
-        heap[i] = heap[c];
-        i = c;
-      }
-      if (hs > 0) heap[i] = last;
-      const int node = top.node;
-      const int d = s_dep[node];
-      if (d >= D) continue;
-      int take = staged ? c_cap[d] : ((caps != nullptr) ? caps[d] : K);
-      if (take > K) take = K;
-      if (take > budget - n) take = budget - n;
-      for (int j = 0; j < take; ++j) {
-        const double cum = -top.key + static_cast<double>(lp_tab[d * K + j]);
-        s_tok[n] = tok_tab[d * K + j];
-        s_par[n] = node;
-        s_dep[n] = d + 1;
-        // push
-        HeapItem it{-cum, ++order, n};
-        int h = hs++;
-        while (h > 0) {
-          const int par = (h - 1) >> 1;
-          if (!heap_less(it, heap[par])) break;
-          heap[h] = heap[par];
-          h = par;
-        }
-        heap[h] = it;
-        ++n;
-      }
+  }
+  __syncthreads();
+  for (int it = 0; it <= kMaxNodes && n < budget; ++it) {
+    double k = alive ? my_key : INFINITY;
+    int ix = alive ? tid : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const double ok = __shfl_xor_sync(0xffffffffu, k, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+      if (ok < k || (ok == k && oi < ix)) { k = ok; ix = oi; }
     }
+    const int buf = it & 1;
+    if (lane == 0) { r_key[buf][warp] = k; r_idx[buf][warp] = ix; }
+    __syncthreads();
+    k = r_key[buf][0];
+    ix = r_idx[buf][0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      const double ok = r_key[buf][w];
+      const int oi = r_idx[buf][w];
+      if (ok < k || (ok == k && oi < ix)) { k = ok; ix = oi; }
+    }
+    if (ix == 0x7fffffff) break;                 // nothing left to pop
+    if (tid == ix) alive = false;
+    const int d = s_dep[ix];
+    if (d >= D) continue;
+    int take = staged ? c_cap[d] : ((caps != nullptr) ? caps[d] : K);
+    if (take > K) take = K;
+    if (take > budget - n) take = budget - n;
+    const int jc = tid - n;                      // thread n + j creates child j
+    if (jc >= 0 && jc < take) {
+      const double cum = -k + static_cast<double>(lp_tab[d * K + jc]);
+      s_tok[tid] = tok_tab[d * K + jc];
+      s_par[tid] = ix;
+      s_dep[tid] = d + 1;
+      my_key = -cum;
+      alive = true;
+    }
+    if (take > 0 && d + 1 > max_dep) max_dep = d + 1;
+    n += take;
+  }
+  if (tid == 0) {
     s_n = n;
     state[ST_NNODES] = n;
   }
@@ -133,9 +134,7 @@ tree_build_kernel(const int* topk_tok, const float* topk_lp, const int* caps, in
     for (int w = 0; w < kMaxWords; ++w) s_bits[i][w] = bits[w];
   }
   __syncthreads();
-  const int n = s_n;
-  int last_pos = past;
-  for (int i = 0; i < n; ++i) last_pos = max(last_pos, past + s_dep[i]);   // cheap: n <= 256
+  const int last_pos = past + max_dep;
   for (int i = tid; i < NB; i += blockDim.x) {
     const bool real = i < n;
     tokens[i] = real ? s_tok[i] : 0;

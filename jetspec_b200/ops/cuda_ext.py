@@ -501,7 +501,7 @@ def moe_route(router_logits: torch.Tensor, top_k: int, renorm: bool, pdl: bool =
 
 
 def moe_route_sort(router_logits: torch.Tensor, top_k: int, renorm: bool, first_expert: int, n_local: int,
-                   pdl: bool = False):
+                   pdl: bool = False, with_tokens: bool = False):
     """Routing plus the stable permutation of the (token, choice) pairs by local expert, all on the device.
     Returns ``(order int32 (T*k), row_weight fp32 (T*k), group_off int32 (n_local+1), counts_all int32 (E))``."""
     lib = load()
@@ -513,9 +513,12 @@ def moe_route_sort(router_logits: torch.Tensor, top_k: int, renorm: bool, first_
     row_w = torch.empty(P, dtype=torch.float32, device=dev)
     group_off = torch.empty(n_local + 1, dtype=torch.int32, device=dev)
     counts_all = torch.empty(E, dtype=torch.int32, device=dev)
+    tok = torch.empty(P, dtype=torch.int32, device=dev) if with_tokens else None
     lib.js_moe_sort.restype = ctypes.c_int
     _check(lib.js_moe_sort(_p(idx), _p(wts), P, E, int(first_expert), int(n_local), _p(order), _p(row_w), _p(group_off),
-                           _p(counts_all), int(pdl), _stream()), "js_moe_sort")
+                           _p(counts_all), int(top_k), _p(tok), int(pdl), _stream()), "js_moe_sort")
+    if with_tokens:
+        return order, row_w, group_off, counts_all, tok
     return order, row_w, group_off, counts_all
 
 
@@ -569,10 +572,10 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
         router_logits = gemm(x, gate_w, epi=EPI_STORE_F32) if gemm_supported(T, E, H) else torch.nn.functional.linear(x, gate_w)
     on_device = E <= 256 and T * top_k <= 16384
     if on_device:    # router + permutation kernels: int32 order, no host synchronisation, static shapes
-        order, row_w, group_off, _ = moe_route_sort(router_logits.float(), top_k, renorm, 0, E)
+        order, row_w, group_off, _, tok = moe_route_sort(router_logits.float(), top_k, renorm, 0, E, with_tokens=True)
     else:
         order, row_w, group_off, _ = route_and_sort(router_logits, top_k, renorm, 0, E)
-    tok = torch.div(order, top_k, rounding_mode="floor")
+        tok = torch.div(order, top_k, rounding_mode="floor")
     xs = x.index_select(0, tok)
     h = torch.empty(T * top_k, I, dtype=x.dtype, device=x.device)
     ys = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
