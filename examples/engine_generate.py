@@ -1,12 +1,15 @@
 """Paged engine: AR vs batched decode, checking that a batch reproduces per-prompt outputs.
 
     python examples/engine_generate.py [/path/to/model]"""
+import os
 import sys
 
 import torch
 
-from jetspec_b200 import JetSpecEngine, SamplingParams
-from jetspec_b200.models import Qwen3ForCausalLM, tiny_config
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run from a checkout
+
+from jetspec_b200 import JetSpecEngine, SamplingParams  # noqa: E402
+from jetspec_b200.models import Qwen3ForCausalLM, tiny_config  # noqa: E402
 
 if __name__ == "__main__":
     dev = "cuda" if torch.cuda.is_available() else "cpu"

@@ -3,12 +3,15 @@
     python examples/simple_generate.py /path/to/Qwen3-8B "The capital of France is"
 
 Without arguments a tiny random-init model is used so the script runs anywhere (CPU included)."""
+import os
 import sys
 
 import torch
 
-from jetspec_b200 import LLM, SamplingParams
-from jetspec_b200.models import Qwen3ForCausalLM, tiny_config
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run from a checkout
+
+from jetspec_b200 import LLM, SamplingParams  # noqa: E402
+from jetspec_b200.models import Qwen3ForCausalLM, tiny_config  # noqa: E402
 
 if __name__ == "__main__":
     dev = "cuda" if torch.cuda.is_available() else "cpu"

@@ -2,12 +2,17 @@
 against plain greedy decoding (bf16 may flip a near-tie after many exact tokens; fp32 is exact).
 
 Environment: JETSPEC_SWEEP_BUDGETS="8,16,32", JETSPEC_SWEEP_WIDTH=4, JETSPEC_SWEEP_MAXNEW=48."""
+import os
+import sys
+
 import torch
 
-from jetspec_b200 import JetSpecEngine, SamplingParams, TargetEchoTreeDrafter
-from jetspec_b200.models import Qwen3ForCausalLM, tiny_config
-from jetspec_b200.tree import list_algorithms
-from jetspec_b200.utils import env_int, env_str
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run from a checkout
+
+from jetspec_b200 import JetSpecEngine, SamplingParams, TargetEchoTreeDrafter  # noqa: E402
+from jetspec_b200.models import Qwen3ForCausalLM, tiny_config  # noqa: E402
+from jetspec_b200.tree import list_algorithms  # noqa: E402
+from jetspec_b200.utils import env_int, env_str  # noqa: E402
 
 if __name__ == "__main__":
     budgets = [int(b) for b in env_str("JETSPEC_SWEEP_BUDGETS", "8,16,32").split(",")]

@@ -3,12 +3,15 @@
     python examples/tree_generate.py /path/to/Qwen3-8B /path/to/draft-head "prompt"
 
 Without arguments: tiny random target + random head on CPU (lossless, low acceptance)."""
+import os
 import sys
 
 import torch
 
-from jetspec_b200 import JetSpecEngine, SamplingParams, DraftHeadTreeDrafter, load_draft_head
-from jetspec_b200.models import Qwen3ForCausalLM, DraftHeadModel, draft_head_config, tiny_config
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run from a checkout
+
+from jetspec_b200 import JetSpecEngine, SamplingParams, DraftHeadTreeDrafter, load_draft_head  # noqa: E402
+from jetspec_b200.models import Qwen3ForCausalLM, DraftHeadModel, draft_head_config, tiny_config  # noqa: E402
 
 if __name__ == "__main__":
     dev = "cuda" if torch.cuda.is_available() else "cpu"
