@@ -35,6 +35,7 @@ from ..runtime import PagedKVPool, Scheduler, SequenceRequest, build_attn_metada
 from ..sampling import SamplingParams, sample
 from ..tree import (build_from_topk, get_algorithm, gpu_tree_accept, should_extend, splice_extension,
                     tree_accept)
+from ..tree.accept import host_tree_accept
 from ..utils.env import env_flag
 
 TREE_BUCKETS = (16, 32, 64, 128, 192, 256)
@@ -309,13 +310,18 @@ class JetSpecEngine:
             self.pool.free(sid)
 
     def _draft_and_build(self, tree_drafter, algo_obj, committed, target_hidden, D, block_size, tree_width, budget,
-                         prompt_info, profile_table, extend_kwargs):
-        """One drafter call → tree.  Uses the drafter's direct top-k when it has one."""
-        root = int(committed[0, -1])
+                         prompt_info, profile_table, extend_kwargs, root_token: Optional[int] = None):
+        """One drafter call → tree.  Uses the drafter's direct top-k when it has one (and its host-only form,
+        ``propose_topk_at``, when the proposal needs nothing from the device)."""
+        root = int(committed[0, -1]) if root_token is None else int(root_token)
         topk_fn = getattr(tree_drafter, "propose_topk", None)
+        at_fn = getattr(tree_drafter, "propose_topk_at", None)
         caps_fn = getattr(algo_obj, "caps_from_topk", None)
-        if topk_fn is not None and caps_fn is not None and not extend_kwargs:
-            tok, lp = topk_fn(committed, D, tree_width, target_hidden=target_hidden)
+        if (topk_fn is not None or at_fn is not None) and caps_fn is not None and not extend_kwargs:
+            if at_fn is not None:
+                tok, lp = at_fn(int(committed.shape[-1]), D, tree_width)
+            else:
+                tok, lp = topk_fn(committed, D, tree_width, target_hidden=target_hidden)
             tree = build_from_topk(algo_obj.name, root, tok, lp, budget, self.device,
                                    algo_kwargs=_algo_init_kwargs(algo_obj), tree_width=tree_width,
                                    prompt_info=prompt_info, profile_table=profile_table)
@@ -562,15 +568,23 @@ class JetSpecEngine:
                 st = state[r.seq_id]
                 th = st["hidden"].unsqueeze(0) if st["hidden"] is not None else None
                 trees.append(self._draft_and_build(r.tree_drafter, algo_obj, st["committed"].unsqueeze(0), th, D,
-                                                   block_size, tree_width, budget, None, None, None))
+                                                   block_size, tree_width, budget, None, None, None,
+                                                   root_token=r.output_tokens[-1]))
             past = [self.pool.state(r.seq_id).length for r in live]
             logits, hidden, meta = self._forward([r.seq_id for r in live], [t.token_ids for t in trees], past,
                                                  trees=trees, taps=taps)
             cu = meta.cu_q.tolist()
+            # greedy: ONE argmax over the whole ragged batch and one device read; acceptance itself runs on the
+            # host lists the builder left on each tree (no per-sequence launches or synchronisations)
+            host_accept = sp.temperature <= 0.0 and all(t.host is not None for t in trees)
+            greedy_all = logits.argmax(-1).tolist() if host_accept else None
             for b, (r, tree) in enumerate(zip(live, trees)):
                 st = state[r.seq_id]
                 lg = logits[cu[b]:cu[b + 1]]
-                if sp.temperature <= 0.0:
+                if host_accept:
+                    h_tok, h_par, h_dep = tree.host
+                    path_l, acc, corr = host_tree_accept(h_tok, h_par, h_dep, greedy_all[cu[b]:cu[b + 1]])
+                elif sp.temperature <= 0.0:
                     path, acc, corr = gpu_tree_accept(tree.token_ids, lg.argmax(-1), tree.parent_indices, tree.depth,
                                                       max_depth=max(int(tree.depth.max()), 1))
                     path_l, corr = path.tolist(), int(corr)
@@ -579,7 +593,10 @@ class JetSpecEngine:
                 self.pool.commit_path(r.seq_id, past[b], tree.num_nodes, path_l)
                 if st["hidden"] is not None:
                     st["hidden"] = torch.cat((st["hidden"], hidden[cu[b]:cu[b + 1]][path_l]), 0)
-                block = tree.token_ids[path_l[1:]].tolist() + [corr]
+                if tree.host is not None:
+                    block = [tree.host[0][i] for i in path_l[1:]] + [corr]
+                else:
+                    block = tree.token_ids[path_l[1:]].tolist() + [corr]
                 st["committed"] = torch.cat((st["committed"], torch.tensor(block, device=self.device)))
                 st["rounds"] += 1
                 st["acc"].append(acc + 1)

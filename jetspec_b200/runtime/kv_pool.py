@@ -209,11 +209,18 @@ class PagedKVPool:
         ``past + len(path)``.  No KV bytes move.
         """
         st = self._seqs[seq_id]
-        p = torch.as_tensor(path, dtype=torch.long, device=self.device)
-        keep = torch.ones(num_nodes, dtype=torch.bool, device=self.device)
-        keep[p] = False
-        order = torch.cat((p, torch.nonzero(keep, as_tuple=True)[0]))
+        if isinstance(path, (list, tuple)):      # host path: the permutation is built without a device read
+            taken = set(path)
+            order = torch.tensor(list(path) + [i for i in range(num_nodes) if i not in taken], dtype=torch.long,
+                                 device=self.device)
+            n_path = len(path)
+        else:
+            p = torch.as_tensor(path, dtype=torch.long, device=self.device)
+            keep = torch.ones(num_nodes, dtype=torch.bool, device=self.device)
+            keep[p] = False
+            order = torch.cat((p, torch.nonzero(keep, as_tuple=True)[0]))
+            n_path = int(p.numel())
         win = self.slot_map[st.row, past:past + num_nodes]
         self.slot_map[st.row, past:past + num_nodes] = win[order]
-        st.length = past + int(p.numel())
+        st.length = past + n_path
         st.last_used = next(self._clock)

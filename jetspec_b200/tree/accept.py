@@ -86,3 +86,30 @@ def gpu_tree_accept(tree_tokens: torch.Tensor, greedy_targets: torch.Tensor, par
         cur = par[cur]
     acc = int(depths[best].item())
     return chain[max_depth - acc:max_depth + 1].contiguous(), acc, correction
+
+
+def host_tree_accept(tokens, parents, depths, greedy):
+    """Greedy acceptance on Python lists: the rule of :func:`gpu_tree_accept` (a node matches when its token is the
+    target's argmax at its parent and no LATER sibling carries the same token; the deepest fully matching root
+    path wins, lowest index on equal depth) without a kernel launch or a device read.  ``greedy[i]`` is the
+    target's argmax at node ``i``.  Returns ``(path list, accepted_len, correction)``."""
+    n = len(tokens)
+    last = {}
+    for i in range(1, n):
+        last[(parents[i], tokens[i])] = i            # the later of two equal siblings wins
+    ok = [False] * n
+    ok[0] = True
+    best, best_d = 0, 0
+    for i in range(1, n):                            # parents precede children
+        p = parents[i]
+        if 0 <= p < i and ok[p] and tokens[i] == greedy[p] and last[(p, tokens[i])] == i:
+            ok[i] = True
+            if depths[i] > best_d:
+                best, best_d = i, depths[i]
+    path = []
+    c = best
+    while c >= 0:
+        path.append(c)
+        c = parents[c]
+    path.reverse()
+    return path, best_d, int(greedy[best])

@@ -72,6 +72,7 @@ def tree_from_lists(tokens, parents, depths, cums, device) -> DraftTree:
         child_maps=child_maps_from_lists(tokens, parents),
         ancestor=anc_t.to(device, non_blocking=True),
         ancestor_packed=anc_t.to(torch.uint8).to(device, non_blocking=True),
+        host=(list(tokens), list(parents), list(depths)),
     )
 
 
@@ -94,7 +95,7 @@ def topk_rows(draft_logits: torch.Tensor, width: int):
 
 
 def _rows(x):
-    return x.tolist() if torch.is_tensor(x) else [list(r) for r in x]
+    return x.tolist() if hasattr(x, "tolist") else [list(r) for r in x]      # tensors and numpy arrays alike
 
 
 def build_from_topk(name: str, root_token: int, topk_tokens, topk_logprobs, budget: int, device,

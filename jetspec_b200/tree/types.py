@@ -25,6 +25,7 @@ class DraftTree:
     ancestor: Optional[torch.Tensor] = None         # (N, N) bool, self-inclusive
     ancestor_packed: Optional[torch.Tensor] = None  # (N, N) uint8
     ancestor_mask: Optional[torch.Tensor] = None    # optional engine-side precomputed mask
+    host: Optional[tuple] = None                    # (tokens, parents, depths) as Python lists when the builder ran on the host
 
 
 class TreeAlgorithm(ABC):

@@ -50,6 +50,17 @@ def test_gemm_tile_widths_and_residual(ext, bn):
     assert rel_err(out, ref) < BF16_TOL
 
 
+def test_gemm_many_row_tiles_picks_wide_tiles(ext):
+    """>= 512 rows (prefill, batched verify): the picker switches to 128x256 tiles with the deep pipeline."""
+    M, N, K = 640, 768, 1024
+    assert ext.pick_gemm_config(M, N, K, ext.EPI_STORE) == (256, 1, 1)
+    x, w, r = rnd(M, K, seed=3), rnd(N, K, scale=0.05, seed=4), rnd(M, N, seed=5)
+    out = ext.gemm(x, w, residual=r)
+    torch.cuda.synchronize()
+    assert rel_err(out, x.float() @ w.float().t() + r.float()) < BF16_TOL
+    ext.check_status("cuda")
+
+
 def test_gemm_fp32_out(ext):
     x, w = rnd(64, 512, seed=6), rnd(128, 512, scale=0.05, seed=7)
     out = ext.gemm(x, w, epi=ext.EPI_STORE_F32, split=2)

@@ -143,3 +143,25 @@ def test_extension_helpers():
     with pytest.raises(ValueError):
         splice_extension(t, 0, ext, ext_budget=1, tree_width=2)
     assert splice_extension(t, 2, ext, ext_budget=0, tree_width=2) is t
+
+
+def test_host_accept_matches_vectorised_accept():
+    """The list-based greedy acceptance used by the batched engine path equals the tensor version on random
+    trees, including duplicate siblings (the later one wins) and ties in depth (the lower index wins)."""
+    import random
+    import torch
+    from jetspec_b200.tree.accept import gpu_tree_accept, host_tree_accept
+    rng = random.Random(0)
+    for trial in range(200):
+        n = rng.randint(1, 24)
+        tokens, parents, depths = [rng.randint(0, 3)], [-1], [0]
+        for i in range(1, n):
+            p = rng.randint(0, i - 1)
+            parents.append(p)
+            depths.append(depths[p] + 1)
+            tokens.append(rng.randint(0, 3))
+        greedy = [rng.randint(0, 3) for _ in range(n)]
+        path_h, acc_h, corr_h = host_tree_accept(tokens, parents, depths, greedy)
+        path_g, acc_g, corr_g = gpu_tree_accept(torch.tensor(tokens), torch.tensor(greedy), torch.tensor(parents),
+                                                torch.tensor(depths), max_depth=max(max(depths), 1))
+        assert path_h == path_g.tolist() and acc_h == acc_g and corr_h == int(corr_g), (trial, tokens, parents, greedy)
