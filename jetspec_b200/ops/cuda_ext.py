@@ -189,7 +189,7 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None)
     if key in GEMM_TUNING:
         return GEMM_TUNING[key]
     m_tiles = (M + 127) // 128
-    if bn is None and epi == EPI_STORE and m_tiles >= 4 and N % 256 == 0:
+    if bn is None and epi == EPI_STORE and m_tiles >= 4 and N % 256 == 0 and m_tiles * (N // 256) >= 64:
         # prefill / batched verify (>= 512 rows): compute bound, and a 128x128 tile asks more of the L2-to-SM path
         # than it gives; 128x256 tiles with the deep pipeline measured 5-12 % faster at 2048 rows
         # (qkv 97 -> 91 us, o 62 -> 56, down 182 -> 165) and equal or better at 512
