@@ -51,9 +51,11 @@ def test_gemm_tile_widths_and_residual(ext, bn):
 
 
 def test_gemm_many_row_tiles_picks_wide_tiles(ext):
-    """>= 512 rows (prefill, batched verify): the picker switches to 128x256 tiles with the deep pipeline."""
-    M, N, K = 640, 768, 1024
+    """Many row tiles (prefill, batched verify): the picker switches to 128x256 tiles with the deep pipeline
+    as long as that still leaves at least 64 CTAs."""
+    M, N, K = 2000, 1024, 512
     assert ext.pick_gemm_config(M, N, K, ext.EPI_STORE) == (256, 1, 1)
+    assert ext.pick_gemm_config(512, 1024, K, ext.EPI_STORE)[0] == 128
     x, w, r = rnd(M, K, seed=3), rnd(N, K, scale=0.05, seed=4), rnd(M, N, seed=5)
     out = ext.gemm(x, w, residual=r)
     torch.cuda.synchronize()
