@@ -4,6 +4,7 @@
     python bench/kernel_cases.py attention   # paged tree attention, 128 nodes over a 1.5k-token prefix
     python bench/kernel_cases.py lm_head     # vocabulary GEMM with the argmax epilogue
     python bench/kernel_cases.py nvfp4       # activation quantiser + block-scaled GEMM on the same four shapes
+    python bench/kernel_cases.py round_small # RMSNorm, norm+RoPE+KV scatter, draft top-k, tree build, accept+commit, KV compaction
 
 Each case holds well under a few GB on the device and launches its kernel a handful of times, so a
 profiler capture of it ends by itself.
@@ -76,8 +77,59 @@ def case_attention(reps: int = 2):
     torch.cuda.synchronize()
 
 
+def case_round_small(reps: int = 2):
+    """The small kernels of a decode round at Qwen3-8B sizes: RMSNorm, per-head norm + RoPE + KV scatter, the
+    draft head's vocabulary top-k (GEMM epilogue + merge), device tree build, accept + commit, KV compaction."""
+    import ctypes
+    import random
+    lib = X.load()
+    dev = "cuda"
+    Hq, Hkv, D, H, S, T = 32, 8, 128, 4096, 8192, 128
+    x, wn = bf(T, H), bf(H)
+    qkv = bf(T, (Hq + 2 * Hkv) * D)
+    qn, kn = bf(D), bf(D)
+    kp, vp, q = bf(Hkv, S, D), bf(Hkv, S, D), torch.empty(T, Hq, D, dtype=torch.bfloat16, device=dev)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    past = 1536
+    positions = i32([past + (i % 20) for i in range(T)])
+    slots = torch.randperm(S, device=dev)[:T].to(torch.int32)
+    freq = X.inv_freq(D, 1e6, dev)
+    h21, wv = bf(21, H), bf(151936, H, scale=0.02)
+    rng = random.Random(0)
+    Dd, K, NB, W, max_len = 20, 7, 128, 4, 4096
+    tk = i32([[rng.randrange(151936) for _ in range(K)] for _ in range(Dd)])
+    lp = torch.tensor([sorted((-rng.random() * 4 for _ in range(K)), reverse=True) for _ in range(Dd)],
+                      dtype=torch.float32, device=dev)
+    caps = i32([K] * Dd)
+    committed = torch.zeros(max_len, dtype=torch.int32, device=dev)
+    slot_row = torch.randperm(max_len, device=dev).to(torch.int32)
+    o = {k: torch.zeros(NB, dtype=torch.int32, device=dev) for k in ("tok", "par", "dep", "pos", "slot")}
+    bits = torch.zeros(NB, W, dtype=torch.int32, device=dev)
+    zero, eos = i32([0]), i32([-1])
+    path_idx, result = torch.zeros(64, dtype=torch.int32, device=dev), torch.zeros(64, dtype=torch.int32, device=dev)
+    st = X.status_word(dev)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    keep = i32([0, 3, 9, 17, 40])
+    for _ in range(reps):
+        X.rmsnorm(x, wn, 1e-6)
+        X.qkv_post(qkv, qn, kn, positions, slots, freq, q, kp, vp, Hq, Hkv, 1e-6)
+        X.lm_head_topk_logprobs(h21, wv, K)
+        state = i32([past, 0, 0, 0, 0, 0, 0, 0])
+        s = X._stream()
+        X._check(lib.js_tree_build(p(tk), p(lp), p(caps), Dd, K, 128, NB, W, p(committed), p(state), p(slot_row), p(zero),
+                                   max_len, p(o["tok"]), p(o["par"]), p(o["dep"]), p(o["pos"]), p(o["slot"]), p(bits),
+                                   p(st), 0, s), "js_tree_build")
+        greedy = o["tok"].roll(-1).contiguous()          # node i+1's token as the target's pick at node i
+        X._check(lib.js_tree_accept_commit(p(o["tok"]), p(o["par"]), p(o["dep"]), p(greedy), NB, p(state), p(slot_row),
+                                           p(zero), max_len, p(committed), max_len, p(eos), 1, 1 << 20, p(path_idx),
+                                           p(result), p(st), 0, s), "js_tree_accept_commit")
+        X.kv_compact(kp[:, :4096].contiguous(), vp[:, :4096].contiguous(), past, keep)
+    torch.cuda.synchronize()
+
+
 if __name__ == "__main__":
     X.load()
-    {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4}[sys.argv[1]]()
+    {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4,
+     "round_small": case_round_small}[sys.argv[1]]()
     X.check_status("cuda")
     print("ok")
