@@ -600,26 +600,72 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         p.part_idx[o] = best_i;
       }
     } else {  // EPI_TOPK: top-8 values + indices and (max, sum exp) over this tile's columns
-      float tv[kTopK];
-      int ti[kTopK];
+      // One thread owns a row, and with a few valid rows (a 21-row draft block) one warp does all the work, so the
+      // cost is the LENGTH of the dependent chains, not the instruction count.  The sorted insertion therefore runs
+      // as four independent chains (columns j % 4, each with its own top-8) that the scheduler interleaves, merged
+      // once at the end; the log-sum-exp takes a chunk maximum first and then 32 independent exponentials.
+      // Order everywhere: larger value first, lower column index first among equal values.
+      constexpr int kChains = 4;
+      float tv[kChains][kTopK];
+      int ti[kChains][kTopK];
 #pragma unroll
-      for (int t = 0; t < kTopK; ++t) { tv[t] = -INFINITY; ti[t] = 0x7fffffff; }
+      for (int c = 0; c < kChains; ++c)
+#pragma unroll
+        for (int t = 0; t < kTopK; ++t) { tv[c][t] = -INFINITY; ti[c][t] = 0x7fffffff; }
       float mx = -INFINITY, se = 0.f;
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         load_chunk(c0, v);
+        const int gc0 = n0 + c0;
+        float cm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gc0 + j < p.N) cm = fmaxf(cm, v[j]);
+        if (cm != -INFINITY) {
+          float cs = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (gc0 + j < p.N) cs += __expf(v[j] - cm);
+          const float nm = fmaxf(mx, cm);
+          se = (mx == -INFINITY ? 0.f : se * __expf(mx - nm)) + cs * __expf(cm - nm);
+          mx = nm;
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int gc = n0 + c0 + j;
-          if (gc >= p.N) continue;
-          const float x = v[j];
-          if (x > mx) { se = se * __expf(mx - x) + 1.f; mx = x; } else { se += __expf(x - mx); }
-          if (x > tv[kTopK - 1]) {
-            // insertion into the sorted list (descending; ties keep the lower index first)
-            float cv = x; int ci = gc;
+          constexpr int kLast = kTopK - 1;
+          const int c = j & (kChains - 1);
+          const int gc = gc0 + j;
+          float cv = gc < p.N ? v[j] : -INFINITY;      // a column past the vocabulary never enters
+          int ci = gc;
+          (void)kLast;
+          // Branch-free compare-exchange down the list (selects only), so the four chains interleave.  Within a
+          // chain columns arrive in increasing order, so "strictly larger" keeps the lower index first.
 #pragma unroll
-            for (int t = 0; t < kTopK; ++t) {
-              if (cv > tv[t]) { const float sv = tv[t]; const int si = ti[t]; tv[t] = cv; ti[t] = ci; cv = sv; ci = si; }
+          for (int t = 0; t < kTopK; ++t) {
+            const bool up = cv > tv[c][t];
+            const float sv = tv[c][t];
+            const int si = ti[c][t];
+            tv[c][t] = up ? cv : sv;
+            ti[c][t] = up ? ci : si;
+            cv = up ? sv : cv;
+            ci = up ? si : ci;
+          }
+        }
+      }
+      // fold chains 1..3 into chain 0 (each list is sorted, so a chain is done at its first entry that cannot enter)
+#pragma unroll
+      for (int c = 1; c < kChains; ++c) {
+#pragma unroll
+        for (int e = 0; e < kTopK; ++e) {
+          float cv = tv[c][e];
+          int ci = ti[c][e];
+          const bool enters = cv > tv[0][kTopK - 1] || (cv == tv[0][kTopK - 1] && ci < ti[0][kTopK - 1]);
+          if (!enters) break;
+#pragma unroll
+          for (int t = 0; t < kTopK; ++t) {
+            if (cv > tv[0][t] || (cv == tv[0][t] && ci < ti[0][t])) {
+              const float sv = tv[0][t]; const int si = ti[0][t];
+              tv[0][t] = cv; ti[0][t] = ci; cv = sv; ci = si;
             }
           }
         }
@@ -627,7 +673,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (grow < p.M) {
         const size_t o = static_cast<size_t>(grow) * gridDim.x + blockIdx.x;
 #pragma unroll
-        for (int t = 0; t < kTopK; ++t) { p.part_val[o * kTopK + t] = tv[t]; p.part_idx[o * kTopK + t] = ti[t]; }
+        for (int t = 0; t < kTopK; ++t) { p.part_val[o * kTopK + t] = tv[0][t]; p.part_idx[o * kTopK + t] = ti[0][t]; }
         p.part_lse[o * 2] = mx;
         p.part_lse[o * 2 + 1] = se;
       }
