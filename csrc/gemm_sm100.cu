@@ -72,6 +72,10 @@ struct GemmParams {
   float w_scale;
   // EPI_ALLREDUCE: only push the partial tile and bump the flags; a finishing kernel reduces (no wait in this kernel)
   int ar_push_only;
+  // Tile order: 0 = column tiles fastest (consecutive CTAs share the activation tile), 1 = row tiles fastest
+  // (consecutive CTAs share the WEIGHT tile: for a vocabulary matrix larger than L2 and many row tiles, each
+  // weight tile then comes from HBM once instead of once per row tile)
+  int m_fast;
 };
 
 JS_DEVICE void red_release_sys_add(int* addr, int v) {
@@ -156,8 +160,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int split = grouped ? 1 : gridDim.z;
   const int z = grouped ? 0 : blockIdx.z;    // == rank in the (1,1,split) cluster
   const int expert = grouped ? blockIdx.z : 0;
-  const int n0 = blockIdx.x * BN;
-  const int m0 = grouped ? p.group_off[expert] + blockIdx.y * BM : blockIdx.y * BM;
+  int bx = blockIdx.x, by = blockIdx.y;        // column tile, row tile
+  if (!grouped && p.m_fast) {
+    const int lin = blockIdx.y * gridDim.x + blockIdx.x;
+    by = lin % static_cast<int>(gridDim.y);
+    bx = lin / static_cast<int>(gridDim.y);
+  }
+  const int n0 = bx * BN;
+  const int m0 = grouped ? p.group_off[expert] + by * BM : by * BM;
   const int m_end = grouped ? p.group_off[expert + 1] : p.M;
   const int wn0 = expert * p.N + n0;         // row of this tile in the (stacked) weight matrix
   if (m0 >= m_end) return;                   // this expert has fewer row tiles (uniform for the CTA)
@@ -595,7 +605,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       if (grow < p.M) {
-        const size_t o = static_cast<size_t>(grow) * gridDim.x + blockIdx.x;
+        const size_t o = static_cast<size_t>(grow) * gridDim.x + bx;
         p.part_val[o] = best;
         p.part_idx[o] = best_i;
       }
@@ -671,7 +681,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       if (grow < p.M) {
-        const size_t o = static_cast<size_t>(grow) * gridDim.x + blockIdx.x;
+        const size_t o = static_cast<size_t>(grow) * gridDim.x + bx;
 #pragma unroll
         for (int t = 0; t < kTopK; ++t) { p.part_val[o * kTopK + t] = tv[0][t]; p.part_idx[o * kTopK + t] = ti[0][t]; }
         p.part_lse[o * 2] = mx;
@@ -798,6 +808,7 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, bn)) return -16;
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace,
                nullptr, nullptr, 0, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr};
+  p.m_fast = ((epi == EPI_ARGMAX || epi == EPI_TOPK) && M > BM) ? 1 : 0;
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
     return deep == 2 ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \

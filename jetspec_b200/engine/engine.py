@@ -514,6 +514,7 @@ class JetSpecEngine:
                 d.reset_cache()
         sched = self._make_scheduler(len(prompts), max_batch_size)
         state, reqs = {}, {}
+        batch_graph = env_flag("JETSPEC_BATCH_GRAPH", True)     # graph-replayed verify forward for the whole batch
         for i, row in enumerate(id_rows):
             r = SequenceRequest(seq_id=self._new_seq_id(), input_ids=row.tolist(), max_new_tokens=sp.max_new_tokens,
                                 temperature=sp.temperature, use_tree=True, tree_drafter=drafters[i],
@@ -571,17 +572,32 @@ class JetSpecEngine:
                                                    block_size, tree_width, budget, None, None, None,
                                                    root_token=r.output_tokens[-1]))
             past = [self.pool.state(r.seq_id).length for r in live]
-            logits, hidden, meta = self._forward([r.seq_id for r in live], [t.token_ids for t in trees], past,
-                                                 trees=trees, taps=taps)
-            cu = meta.cu_q.tolist()
-            # greedy: ONE argmax over the whole ragged batch and one device read; acceptance itself runs on the
-            # host lists the builder left on each tree (no per-sequence launches or synchronisations)
-            host_accept = sp.temperature <= 0.0 and all(t.host is not None for t in trees)
-            greedy_all = logits.argmax(-1).tolist() if host_accept else None
+            graph_verify = False
+            if self.use_kernels and sp.temperature <= 0.0 and batch_graph:
+                from .fast_round import FastRound
+                fast = FastRound.get(self)
+                graph_verify = fast.supports_batch_verify(trees, taps)
+            if graph_verify:
+                # the whole verify forward of all live trees is one graph replay; the logits are never written
+                greedy_seq, hidden = fast.batch_verify([r.seq_id for r in live], trees, past, n_max, taps)
+                nb = hidden.shape[0] // len(live) if hidden is not None else 0
+                cu = [b * nb for b in range(len(live) + 1)]
+                logits, host_accept, greedy_all = None, True, None
+            else:
+                logits, hidden, meta = self._forward([r.seq_id for r in live], [t.token_ids for t in trees], past,
+                                                     trees=trees, taps=taps)
+                cu = meta.cu_q.tolist()
+                # greedy: ONE argmax over the whole ragged batch and one device read; acceptance itself runs on
+                # the host lists the builder left on each tree (no per-sequence launches or synchronisations)
+                host_accept = sp.temperature <= 0.0 and all(t.host is not None for t in trees)
+                greedy_all = logits.argmax(-1).tolist() if host_accept else None
             for b, (r, tree) in enumerate(zip(live, trees)):
                 st = state[r.seq_id]
-                lg = logits[cu[b]:cu[b + 1]]
-                if host_accept:
+                lg = logits[cu[b]:cu[b + 1]] if logits is not None else None
+                if graph_verify:
+                    h_tok, h_par, h_dep = tree.host
+                    path_l, acc, corr = host_tree_accept(h_tok, h_par, h_dep, greedy_seq[b])
+                elif host_accept:
                     h_tok, h_par, h_dep = tree.host
                     path_l, acc, corr = host_tree_accept(h_tok, h_par, h_dep, greedy_all[cu[b]:cu[b + 1]])
                 elif sp.temperature <= 0.0:
@@ -592,7 +608,7 @@ class JetSpecEngine:
                     path_l, acc, corr = tree_accept(tree, lg.unsqueeze(0), sp.temperature)
                 self.pool.commit_path(r.seq_id, past[b], tree.num_nodes, path_l)
                 if st["hidden"] is not None:
-                    st["hidden"] = torch.cat((st["hidden"], hidden[cu[b]:cu[b + 1]][path_l]), 0)
+                    st["hidden"] = torch.cat((st["hidden"], hidden[cu[b]:cu[b] + tree.num_nodes][path_l]), 0)
                 if tree.host is not None:
                     block = [tree.host[0][i] for i in path_l[1:]] + [corr]
                 else:

@@ -495,6 +495,115 @@ class FastRound:
         r["result_host"].copy_(r["result"], non_blocking=True)
         return n + 4
 
+    # ------------------------------------------------------------------ batched verify (continuous batching)
+    def supports_batch_verify(self, trees, tap_ids) -> bool:
+        cfg = self.cfg
+        if cfg.head_dim != 128 or self.tp is not None or not trees:
+            return False
+        return all(t.host is not None and t.num_nodes <= 256 for t in trees)
+
+    def batch_verify(self, seq_ids, trees, past, nb: int, tap_ids=None):
+        """The verify forward of ``B`` trees (one per live sequence) as ONE graph replay: embedding, the decoder
+        stack on ``B x NB`` rows through the paged pool, final norm and the vocabulary argmax.  The host stages
+        tokens, positions, ancestor bits, slot-map rows and committed lengths in one pinned buffer; one copy in, one
+        copy out.  Returns ``(greedy, hidden)``: per sequence the target's argmax at every node (host lists) and,
+        with ``tap_ids``, the tapped hidden rows ``(B*NB, taps*H)`` on the device (row ``b*NB + i`` = node ``i``).
+
+        A graph is captured per ``(B, NB)``; the first call of a shape runs the kernels once eagerly with the real
+        inputs (idempotent: the same KV rows are written again by the replay)."""
+        import numpy as np
+        from ..tree.ancestor import ancestor_bits_np
+        pool, cfg, dev = self.eng.pool, self.cfg, self.device
+        B = len(seq_ids)
+        NB = int(nb)                      # the tree bucket the caller reserved KV room for
+        if max(t.num_nodes for t in trees) > NB:
+            raise ValueError("a tree is larger than the reserved bucket")
+        W = max(1, (NB + 31) // 32)
+        tap_ids = list(tap_ids) if tap_ids else None
+        key = ("batch", B, NB, tuple(tap_ids or ()), id(pool))
+        r = self.graphs.get(key)
+        fresh = r is None
+        if fresh:
+            H, T = cfg.hidden_size, B * NB
+            n_in = T * (2 + W) + 2 * B
+            r = {"B": B, "NB": NB, "W": W, "tap_ids": tap_ids}
+            r["inp"] = _i32(n_in, dev)
+            r["inp_host"] = torch.zeros(n_in, dtype=torch.int32).pin_memory()
+            r["tokens"], r["positions"] = r["inp"][:T], r["inp"][T:2 * T]
+            r["mask"] = r["inp"][2 * T:2 * T + T * W].view(T, W)
+            r["seq_rows"] = r["inp"][2 * T + T * W:2 * T + T * W + B]
+            r["past"] = r["inp"][2 * T + T * W + B:]
+            r["slots"] = _i32(T, dev)
+            r["cu_q"] = (torch.arange(B + 1, dtype=torch.int32, device=dev) * NB).contiguous()
+            r["ar"] = torch.arange(NB, dtype=torch.long, device=dev)
+            r["greedy"] = _i32(T, dev)
+            r["greedy_host"] = torch.zeros(T, dtype=torch.int32).pin_memory()
+            r["stack"] = _Stack(self.lcfg, T, dev, pool.max_seq_len)
+            r["xn"] = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+            nt = X.n_tiles(self.lm_head_w.shape[0])
+            r["am_ws"] = {"val": torch.zeros(T, nt, dtype=torch.float32, device=dev),
+                          "idx": torch.zeros(T, nt, dtype=torch.int32, device=dev)}
+            r["am_val"] = torch.zeros(T, dtype=torch.float32, device=dev)
+            r["taps"] = torch.zeros(T, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
+        NB, W, T = r["NB"], r["W"], B * r["NB"]
+        h = r["inp_host"].numpy()
+        tok, pos = h[:T].reshape(B, NB), h[T:2 * T].reshape(B, NB)
+        bits = h[2 * T:2 * T + T * W].reshape(B, NB, W)
+        rows, pst = h[2 * T + T * W:2 * T + T * W + B], h[2 * T + T * W + B:]
+        pad_bits = np.zeros((NB, W), dtype=np.uint32)                   # a pad row sees only itself
+        idx = np.arange(NB)
+        pad_bits[idx, idx >> 5] = np.uint32(1) << (idx & 31).astype(np.uint32)
+        pad_bits = pad_bits.view(np.int32)
+        for b, (sid, t) in enumerate(zip(seq_ids, trees)):
+            n = t.num_nodes
+            t_tok, t_par, t_dep = t.host
+            p0 = int(past[b])
+            if p0 + NB > pool.max_seq_len:
+                raise RuntimeError("tree window exceeds the sequence capacity of the pool")
+            tok[b, :n] = t_tok
+            tok[b, n:] = 0
+            pos[b, :n] = np.asarray(t_dep, dtype=np.int32) + p0
+            pos[b, n:] = p0 + max(t_dep)
+            bits[b] = pad_bits
+            bits[b, :n, :max(1, (n + 31) // 32)] = ancestor_bits_np(t_par, n, max(1, (n + 31) // 32)).view(np.int32)
+            rows[b] = pool.state(sid).row
+            pst[b] = p0
+        r["inp"].copy_(r["inp_host"], non_blocking=True)
+        if fresh:
+            self._launch_batch_verify(r, pdl=False)
+            torch.cuda.synchronize()
+            X.check_status(dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch_batch_verify(r, pdl=_PDL)
+            r["graph"] = g
+            pool.frozen = True
+            self.graphs[key] = r
+        r["graph"].replay()
+        torch.cuda.current_stream().synchronize()
+        g_all = r["greedy_host"].numpy().reshape(B, NB)
+        greedy = [g_all[b, :t.num_nodes].tolist() for b, t in enumerate(trees)]
+        return greedy, r["taps"]
+
+    def _launch_batch_verify(self, r, pdl: bool) -> None:
+        pool, cfg = self.eng.pool, self.cfg
+        st = r["stack"]
+        # KV slots of every sequence's tree window: slot_map[row_b, past_b + i]
+        win = r["past"].long()[:, None] + r["ar"][None, :]
+        r["slots"].copy_(pool.slot_map[r["seq_rows"].long()].gather(1, win).reshape(-1))
+        X.embed(r["tokens"], self.embed_w, out=st.x, pdl=False)
+        decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"], r["cu_q"],
+                       r["past"], r["positions"], r["slots"], r["mask"], False, self.freq, taps=r["taps"],
+                       tap_ids=r["tap_ids"], pdl=pdl)
+        X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
+        last = cfg.num_hidden_layers - 1
+        if r["taps"] is not None:
+            for j, t in enumerate(r["tap_ids"]):
+                if t == last:
+                    X.gather_rows(r["xn"], None, r["taps"], dst_col0=j * cfg.hidden_size, pdl=pdl)
+        X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        r["greedy_host"].copy_(r["greedy"], non_blocking=True)
+
     # ------------------------------------------------------------------ sequence setup
     def _begin(self, r, sid: int, ids: torch.Tensor, taps, total: int) -> int:
         """Prefill through the eager kernel path and initialise the round's device state."""

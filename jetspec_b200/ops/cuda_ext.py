@@ -53,16 +53,30 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not os.path.isdir(_CSRC):
         raise RuntimeError(f"kernel sources not found at {_CSRC}")
     os.makedirs(_OUT_DIR, exist_ok=True)
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", _CSRC] + sources() + ["-o", LIB_PATH]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-        print(" ".join(cmd), file=sys.stderr)
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed:\n{r.stdout}\n{r.stderr}")
-    if verbose:
-        print(r.stderr, file=sys.stderr)
+    # Several ranks may find the library stale at the same moment: one builds under a file lock, into a
+    # temporary name that replaces the library atomically; the others wait and then find it fresh.
+    import fcntl
+    with open(os.path.join(_OUT_DIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale():
+                return LIB_PATH
+            nvcc = os.environ.get("NVCC", "nvcc")
+            tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+            cmd = [nvcc] + NVCC_FLAGS + ["-I", _CSRC] + sources() + ["-o", tmp]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+                print(" ".join(cmd), file=sys.stderr)
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError(f"nvcc failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp, LIB_PATH)
+            if verbose:
+                print(r.stderr, file=sys.stderr)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

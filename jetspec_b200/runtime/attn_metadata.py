@@ -61,9 +61,12 @@ def build_attn_metadata(pool, seq_ids: Sequence[int], past_lens: Sequence[int],
             pos[s:e] = past + np.arange(e - s, dtype=np.int32)
         else:
             t = trees[b]
-            pos[s:e] = past + t.depth.cpu().numpy().astype(np.int32)
+            host = getattr(t, "host", None)          # builder's own lists: no device read per sequence
+            depth_h = np.asarray(host[2], dtype=np.int32) if host is not None else t.depth.cpu().numpy().astype(np.int32)
+            parents_h = host[1] if host is not None else t.parent_indices.tolist()
+            pos[s:e] = past + depth_h
             bits[s:e, : max(1, (counts[b] + 31) // 32)] = ancestor_bits_np(
-                t.parent_indices.tolist(), counts[b], max(1, (counts[b] + 31) // 32))
+                parents_h, counts[b], max(1, (counts[b] + 31) // 32))
         slot_rows.append(pool.slot_map[int(rows[b]), past:past + (e - s)])
     slots = torch.cat(slot_rows) if slot_rows else torch.zeros(0, dtype=torch.int32, device=device)
     to = lambda a: torch.from_numpy(a).to(device)
