@@ -28,13 +28,13 @@ def prompt():
 def teacher_forced_agreement(model, prompt, new_ids):
     """Fraction of generated tokens equal to the argmax of one fp32 causal forward over prompt+output,
     and the worst logit shortfall of a disagreeing token (relative to the row's max |logit|)."""
+    import copy
     from jetspec_b200.core.model_runner import ModelRunner
-    ref = ModelRunner(model.float())
-    try:
-        ids = torch.cat((prompt.to("cuda"), torch.tensor([new_ids], device="cuda")), 1)
-        logits, _, _ = ref.forward(ids)
-    finally:
-        model.bfloat16()
+    # an fp32 COPY: converting the engine's own model in place would move its parameters to new storage under
+    # the captured graphs, which keep reading the old addresses
+    ref = ModelRunner(copy.deepcopy(model).float())
+    ids = torch.cat((prompt.to("cuda"), torch.tensor([new_ids], device="cuda")), 1)
+    logits, _, _ = ref.forward(ids)
     T = prompt.shape[1]
     rows = logits[0, T - 1:T - 1 + len(new_ids)].float()
     pick = torch.tensor(new_ids, device="cuda")
@@ -158,4 +158,32 @@ def test_moe_target_runs_on_the_kernel_path_and_is_lossless():
                             sampling_params=sp, return_stats=True)
     assert len(ar) == 24 and out["token_ids"] == ar
     from jetspec_b200.ops import cuda_ext
+    cuda_ext.check_status("cuda")
+
+
+def test_batched_graph_verify_is_lossless_and_matches_the_eager_batch(engine, small, monkeypatch):
+    """Continuous batching with the verify forward of all live trees as one graph replay: every request's tokens
+    equal its own single-request greedy decode, with and without a draft head feeding on tapped hidden states,
+    and the eager batched forward (``JETSPEC_BATCH_GRAPH=0``) gives the same tokens."""
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter, DraftHeadTreeDrafter
+    from jetspec_b200.models import DraftHeadModel, draft_head_config
+    from jetspec_b200.engine.fast_round import FastRound
+    from jetspec_b200.ops import cuda_ext
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 4096, (1, n), generator=g) for n in (17, 40, 9, 64)]
+    sp = SamplingParams(0.0, 20)
+    singles = [engine.generate(p, sp)["token_ids"] for p in prompts]
+    kw = dict(block_size=5, tree_width=3, budget=16, sampling_params=sp, return_stats=True)
+    outs = engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=7), **kw)
+    assert any(k[0] == "batch" for k in FastRound.get(engine).graphs if isinstance(k, tuple) and k)
+    assert [o["token_ids"] for o in outs] == singles
+    hcfg = draft_head_config(small.config, num_layers=1, block_size=5, num_taps=3)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+    drafters = [DraftHeadTreeDrafter(head, small, block_size=5) for _ in prompts]
+    houts = engine.generate_tree_batch(prompts, drafters, target_layer_ids=head.target_layer_ids, **kw)
+    assert [o["token_ids"] for o in houts] == singles
+    monkeypatch.setenv("JETSPEC_BATCH_GRAPH", "0")
+    eouts = engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=7), **kw)
+    agree = sum(a == b for o, s in zip(eouts, singles) for a, b in zip(o["token_ids"], s)) / (20 * len(prompts))
+    assert agree > 0.9            # a different forward (separate projections): bf16 near-ties may flip late tokens
     cuda_ext.check_status("cuda")
