@@ -55,6 +55,15 @@ def bucket_for_n(n: int) -> int:
     return ((n + step - 1) // step) * step
 
 
+class _OneNode:
+    """A one-node tree (the last committed token) for autoregressive steps through the batched verify graph."""
+    __slots__ = ("host", "num_nodes")
+
+    def __init__(self, token: int):
+        self.host = ([int(token)], [-1], [0])
+        self.num_nodes = 1
+
+
 def _round_session_capacity(prompt_len: int) -> int:
     return ((int(prompt_len) + 255) // 256) * 256
 
@@ -466,9 +475,17 @@ class JetSpecEngine:
             self.last_stats["steps"] += 1
             self.last_stats["max_batch"] = max(self.last_stats["max_batch"], len(ready))
             past = [self.pool.state(r.seq_id).length for r in ready]
-            toks = [torch.tensor(r.input_ids[-1:], device=self.device) for r in ready]
-            logits, _, _ = self._forward([r.seq_id for r in ready], toks, past)
-            nxt = sample(logits, sp.temperature).tolist()
+            if self.use_kernels and sp.temperature <= 0.0 and self.cfg.head_dim == 128 \
+                    and getattr(self, "tp", None) is None and env_flag("JETSPEC_BATCH_GRAPH", True):
+                # one graph replay per decode step: every sequence contributes a one-node "tree"
+                from .fast_round import FastRound
+                nodes = [_OneNode(r.input_ids[-1]) for r in ready]
+                greedy, _ = FastRound.get(self).batch_verify([r.seq_id for r in ready], nodes, past, 1)
+                nxt = [g[0] for g in greedy]
+            else:
+                toks = [torch.tensor(r.input_ids[-1:], device=self.device) for r in ready]
+                logits, _, _ = self._forward([r.seq_id for r in ready], toks, past)
+                nxt = sample(logits, sp.temperature).tolist()
             for r, p, t in zip(ready, past, nxt):
                 self.pool.state(r.seq_id).length = p + 1
                 self.pool.touch(r.seq_id)
