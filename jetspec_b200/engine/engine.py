@@ -147,11 +147,14 @@ class JetSpecEngine:
                 and self.pool.max_seqs >= seqs
             if fits:
                 return self.pool
-            if self.pool.frozen:
-                raise RuntimeError("KV pool is frozen by live CUDA graphs and cannot grow; "
-                                   "construct the engine with a larger num_pages / max_seq_len")
             if self.pool.resident():
                 raise RuntimeError("cannot resize the KV pool while sequences are resident")
+            if self.pool.frozen and self._tree_session is not None:
+                # a session promised stable shapes: growing would silently drop its captured graphs
+                raise RuntimeError("KV pool is frozen by live CUDA graphs and cannot grow; "
+                                   "construct the engine with a larger num_pages / max_seq_len")
+            # frozen but idle and outside a session: the graphs captured against the old pool are dropped with it
+            # (self._fast below) and captured again on demand
         world = self.tp.world if getattr(self, "tp", None) is not None else 1
         self.pool = PagedKVPool(self.cfg.num_hidden_layers, self.cfg.num_key_value_heads // world, self.cfg.head_dim,
                                 max(want_pages, 2), page_size=self.block_size,
