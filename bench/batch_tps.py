@@ -57,7 +57,7 @@ def main():
                         max_seq_len=args.prompt_hi + args.new + 2 * args.budget + 64)
     sp = SamplingParams(0.0, args.new)
     # AR batch: the oracle's script and the baseline of the speedup
-    eng.generate_batch(prompts[:2], SamplingParams(0.0, 4))            # warm-up (module load, pool)
+    eng.generate_batch(prompts, SamplingParams(0.0, 3))                # warm-up: module load, pool, graph capture
     _sync()
     t0 = time.perf_counter()
     ar = eng.generate_batch(prompts, sp)
