@@ -101,6 +101,19 @@ def _finish_layer_weights(out: list) -> list:
     return out
 
 
+_WIDE_GU_ROWS = 1024
+
+
+def _gu_wide(L: dict) -> torch.Tensor:
+    """The layer's gate/up weight re-interleaved for 256-column tiles (128 gate + 128 up rows per tile)."""
+    if "gu256" not in L:
+        w, h = L["gu"], L.get("gu_bn", 128) // 2
+        I2, H = w.shape
+        v = w.view(I2 // (2 * h), 2, h, H)
+        L["gu256"] = X.interleave_gate_up(v[:, 0].reshape(I2 // 2, H), v[:, 1].reshape(I2 // 2, H), 256)
+    return L["gu256"]
+
+
 class _Stack:
     """Static activation buffers of one decoder stack for a fixed row count ``T``."""
 
@@ -230,7 +243,12 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             continue
         if pf is not None:
             pf.ahead(L["down"])
-        X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, bn=L.get("gu_bn"), pdl=pdl)
+        if st.T >= _WIDE_GU_ROWS and tp is None:
+            # many row tiles (batched verify, long prefill): compute bound, 128x256 tiles measured 24 % faster at
+            # 2048 rows (519 -> 396 us); the 256-interleaved copy of the weight is made on first use
+            X.gemm(st.h, _gu_wide(L), out=st.act, epi=X.EPI_SWIGLU, bn=256, split=1, deep=0, pdl=pdl)
+        else:
+            X.gemm(st.h, L["gu"], out=st.act, epi=X.EPI_SWIGLU, bn=L.get("gu_bn"), pdl=pdl)
         if pf is not None:
             nxt = layers[li + 1]["qkv"] if li != last else then_prefetch
             if nxt is not None:
