@@ -322,7 +322,8 @@ class JetSpecEngine:
             self.pool.free(sid)
 
     def _draft_and_build(self, tree_drafter, algo_obj, committed, target_hidden, D, block_size, tree_width, budget,
-                         prompt_info, profile_table, extend_kwargs, root_token: Optional[int] = None):
+                         prompt_info, profile_table, extend_kwargs, root_token: Optional[int] = None,
+                         host_only: bool = False):
         """One drafter call → tree.  Uses the drafter's direct top-k when it has one (and its host-only form,
         ``propose_topk_at``, when the proposal needs nothing from the device)."""
         root = int(committed[0, -1]) if root_token is None else int(root_token)
@@ -334,7 +335,7 @@ class JetSpecEngine:
                 tok, lp = at_fn(int(committed.shape[-1]), D, tree_width)
             else:
                 tok, lp = topk_fn(committed, D, tree_width, target_hidden=target_hidden)
-            tree = build_from_topk(algo_obj.name, root, tok, lp, budget, self.device,
+            tree = build_from_topk(algo_obj.name, root, tok, lp, budget, "host" if host_only else self.device,
                                    algo_kwargs=_algo_init_kwargs(algo_obj), tree_width=tree_width,
                                    prompt_info=prompt_info, profile_table=profile_table)
             return tree
@@ -535,6 +536,9 @@ class JetSpecEngine:
         sched = self._make_scheduler(len(prompts), max_batch_size)
         state, reqs = {}, {}
         batch_graph = env_flag("JETSPEC_BATCH_GRAPH", True)     # graph-replayed verify forward for the whole batch
+        # when the graph path is certain to take every tree, trees are built as host lists only (no device tensors)
+        graph_ok = bool(batch_graph and self.use_kernels and sp.temperature <= 0.0 and self.cfg.head_dim == 128
+                        and getattr(self, "tp", None) is None and n_max <= 256)
         for i, row in enumerate(id_rows):
             r = SequenceRequest(seq_id=self._new_seq_id(), input_ids=row.tolist(), max_new_tokens=sp.max_new_tokens,
                                 temperature=sp.temperature, use_tree=True, tree_drafter=drafters[i],
@@ -590,7 +594,7 @@ class JetSpecEngine:
                 th = st["hidden"].unsqueeze(0) if st["hidden"] is not None else None
                 trees.append(self._draft_and_build(r.tree_drafter, algo_obj, st["committed"].unsqueeze(0), th, D,
                                                    block_size, tree_width, budget, None, None, None,
-                                                   root_token=r.output_tokens[-1]))
+                                                   root_token=r.output_tokens[-1], host_only=graph_ok))
             past = [self.pool.state(r.seq_id).length for r in live]
             graph_verify = False
             if self.use_kernels and sp.temperature <= 0.0 and batch_graph:

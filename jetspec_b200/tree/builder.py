@@ -61,6 +61,10 @@ def expand_best_first(root_token: int, topk_tokens, topk_logprobs, caps: Optiona
 
 def tree_from_lists(tokens, parents, depths, cums, device) -> DraftTree:
     n = len(tokens)
+    if isinstance(device, str) and device == "host":
+        # host-only tree for consumers that stage their own device buffers (the batched verify graph): no tensors
+        return DraftTree(token_ids=None, parent_indices=None, depth=None, num_nodes=n,
+                         host=(list(tokens), list(parents), list(depths)))
     anc = ancestor_matrix_np(parents, n)
     anc_t = torch.from_numpy(anc)
     return DraftTree(
