@@ -165,3 +165,15 @@ def test_host_accept_matches_vectorised_accept():
         path_g, acc_g, corr_g = gpu_tree_accept(torch.tensor(tokens), torch.tensor(greedy), torch.tensor(parents),
                                                 torch.tensor(depths), max_depth=max(max(depths), 1))
         assert path_h == path_g.tolist() and acc_h == acc_g and corr_h == int(corr_g), (trial, tokens, parents, greedy)
+
+
+def test_host_only_tree_carries_the_same_lists():
+    """``device="host"`` builds the tree without tensors (for consumers that stage their own device buffers);
+    its lists equal those of the tensor-backed tree."""
+    from jetspec_b200.tree.builder import build_from_topk
+    toks = [[5, 9, 2], [7, 7, 1], [3, 4, 8]]
+    lps = [[-0.1, -2.5, -4.0], [-0.3, -1.5, -3.0], [-0.2, -2.0, -2.5]]
+    full = build_from_topk("accum_logp", 11, toks, lps, 8, "cpu", tree_width=3)
+    host = build_from_topk("accum_logp", 11, toks, lps, 8, "host", tree_width=3)
+    assert host.token_ids is None and host.num_nodes == full.num_nodes
+    assert host.host == full.host == (full.token_ids.tolist(), full.parent_indices.tolist(), full.depth.tolist())
