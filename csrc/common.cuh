@@ -221,6 +221,15 @@ JS_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
 
 // ---------------------------------------------------------------- programmatic dependent launch
 JS_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Named barrier 1 over 128 threads (the four epilogue warps of a GEMM CTA), plain and with an AND reduction.
+JS_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+JS_DEVICE bool epi_bar_and(bool pred) {
+  int out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.s32 %0, 1, 0, p;\n\t}"
+      : "=r"(out) : "r"(static_cast<int>(pred)) : "memory");
+  return out != 0;
+}
 JS_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- small math

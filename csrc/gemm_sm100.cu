@@ -331,6 +331,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 64) JS_TRACE(5);   // every peer's partial has landed here
   }
 
+  if constexpr (EPI == EPI_TOPK) {
+    // the few-rows path below synchronises the four epilogue warps with each other: all of them take it or none
+    if (epi_warp) acc_ok = epi_bar_and(acc_ok);
+  }
   if (epi_warp && acc_ok) {
     const float* recv = reinterpret_cast<const float*>(smem + (alias ? 0 : S::kTiles));
     // fetch 32 consecutive accumulator columns of this thread's row, reduced over the K split
@@ -608,6 +612,91 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const size_t o = static_cast<size_t>(grow) * gridDim.x + bx;
         p.part_val[o] = best;
         p.part_idx[o] = best_i;
+      }
+    } else if (p.M <= 32) {
+      // EPI_TOPK with at most 32 rows (a draft block): all valid rows sit in the lane quadrant of ONE warp, which
+      // would run the whole epilogue alone.  That warp instead drops the tile's logits into shared memory (the
+      // pipeline stages are dead by now), column-major so that a warp touches 32 consecutive floats, and all four
+      // epilogue warps take 32 columns each of every row; the owner warp then merges the four sorted lists.
+      float* buf = reinterpret_cast<float*>(smem);                 // [BN columns][32 rows]
+      float* lst_v = buf + BN * 32;                                // [4 column groups][32 rows][8]
+      int* lst_i = reinterpret_cast<int*>(lst_v + 4 * 32 * kTopK);
+      static_assert(BN == 128, "four column groups of 32");
+      float mx = -INFINITY, se = 0.f;
+      if (quad == 0) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          load_chunk(c0, v);
+          const int gc0 = n0 + c0;
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (gc0 + j >= p.N) v[j] = -INFINITY;                  // a column past the vocabulary never enters
+            cm = fmaxf(cm, v[j]);
+          }
+          if (cm != -INFINITY) {
+            float cs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) cs += __expf(v[j] - cm);  // exp(-inf) = 0 for the masked columns
+            const float nm = fmaxf(mx, cm);
+            se = (mx == -INFINITY ? 0.f : se * __expf(mx - nm)) + cs * __expf(cm - nm);
+            mx = nm;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) buf[(c0 + j) * 32 + lane] = v[j];
+        }
+      }
+      epi_bar_sync();
+      float tv[kTopK];
+      int ti[kTopK];
+#pragma unroll
+      for (int t = 0; t < kTopK; ++t) { tv[t] = -INFINITY; ti[t] = 0x7fffffff; }
+      if (lane < p.M) {
+#pragma unroll 8
+        for (int j = 0; j < 32; ++j) {
+          float cv = buf[(quad * 32 + j) * 32 + lane];
+          int ci = n0 + quad * 32 + j;
+#pragma unroll
+          for (int t = 0; t < kTopK; ++t) {                        // columns ascend: "strictly larger" keeps the lower index first
+            const bool up = cv > tv[t];
+            const float sv = tv[t];
+            const int si = ti[t];
+            tv[t] = up ? cv : sv;
+            ti[t] = up ? ci : si;
+            cv = up ? sv : cv;
+            ci = up ? si : ci;
+          }
+        }
+      }
+      if (quad != 0) {
+#pragma unroll
+        for (int t = 0; t < kTopK; ++t) {
+          lst_v[(quad * 32 + lane) * kTopK + t] = tv[t];
+          lst_i[(quad * 32 + lane) * kTopK + t] = ti[t];
+        }
+      }
+      epi_bar_sync();
+      if (quad == 0 && lane < p.M) {
+        for (int c = 1; c < 4; ++c) {
+          for (int e = 0; e < kTopK; ++e) {
+            float cv = lst_v[(c * 32 + lane) * kTopK + e];
+            int ci = lst_i[(c * 32 + lane) * kTopK + e];
+            const bool enters = cv > tv[kTopK - 1] || (cv == tv[kTopK - 1] && ci < ti[kTopK - 1]);
+            if (!enters) break;
+#pragma unroll
+            for (int t = 0; t < kTopK; ++t) {
+              if (cv > tv[t] || (cv == tv[t] && ci < ti[t])) {
+                const float sv = tv[t]; const int si = ti[t];
+                tv[t] = cv; ti[t] = ci; cv = sv; ci = si;
+              }
+            }
+          }
+        }
+        const size_t o = static_cast<size_t>(grow) * gridDim.x + bx;
+#pragma unroll
+        for (int t = 0; t < kTopK; ++t) { p.part_val[o * kTopK + t] = tv[t]; p.part_idx[o * kTopK + t] = ti[t]; }
+        p.part_lse[o * 2] = mx;
+        p.part_lse[o * 2 + 1] = se;
       }
     } else {  // EPI_TOPK: top-8 values + indices and (max, sum exp) over this tile's columns
       // One thread owns a row, and with a few valid rows (a 21-row draft block) one warp does all the work, so the

@@ -107,8 +107,9 @@ def test_lm_head_argmax(ext):
     assert float((idx.long() == ref_idx).float().mean()) > 0.95
 
 
-def test_lm_head_topk_logprobs(ext):
-    M, V, H, K = 20, 5000, 512, 7
+@pytest.mark.parametrize("M", [20, 32, 100])      # <= 32 rows: the shared-memory epilogue; more: one thread per row
+def test_lm_head_topk_logprobs(ext, M):
+    V, H, K = 5000, 512, 7
     h, w = rnd(M, H, seed=13), rnd(V, H, scale=0.08, seed=14)
     tok, lp = ext.lm_head_topk_logprobs(h, w, K)
     ref_lp_all = torch.log_softmax(h.float() @ w.float().t(), -1)
