@@ -323,12 +323,9 @@ template <int G>
 static int launch_attn(const AttnParams& p, int q_tiles, bool pdl, cudaStream_t stream) {
   constexpr int NPT = AROWS / G;
   const int smem = AROWS * 256 + 4 * AKEYS * 256 + NPT * p.W * 4 + 16;
-  static bool configured = false;
+  static int configured[kMaxDevicesCached] = {};
   auto kern = paged_tree_attn_kernel<G>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess) return -3;
-    configured = true;
-  }
+  if (ensure_dyn_smem(kern, 100 * 1024, configured) != 0) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(q_tiles, p.Hkv, p.splits);
   cfg.blockDim = dim3(ATHREADS);

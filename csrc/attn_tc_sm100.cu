@@ -545,12 +545,9 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
 
 template <int G>
 static int launch_attn_tc(const AttnTcParams& p, int q_tiles, bool pdl, cudaStream_t stream) {
-  static bool configured = false;
+  static int configured[kMaxDevicesCached] = {};
   auto kern = paged_tree_attn_tc_kernel<G>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnTcSmem) != cudaSuccess) return -3;
-    configured = true;
-  }
+  if (ensure_dyn_smem(kern, kAttnTcSmem, configured) != 0) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(q_tiles, p.Hkv, p.splits);
   cfg.blockDim = dim3(TTHREADS);

@@ -34,6 +34,25 @@ JS_DEVICE void report(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// ---------------------------------------------------------------- host: per-device launch attributes
+// cudaFuncSetAttribute applies to the CURRENT device only, so the "already configured" cache of a kernel is one
+// slot per device (a process may drive several GPUs).  `slots` is a zero-initialised static array of
+// kMaxDevicesCached ints owned by the caller; the value is the largest dynamic shared-memory size set so far.
+constexpr int kMaxDevicesCached = 64;
+template <typename Kern>
+inline int ensure_dyn_smem(Kern kern, int bytes, int* slots) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -3;
+  if (dev < 0 || dev >= kMaxDevicesCached) {   // beyond the cache: set it every time
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -3;
+  }
+  if (bytes > __atomic_load_n(&slots[dev], __ATOMIC_ACQUIRE)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -3;
+    __atomic_store_n(&slots[dev], bytes, __ATOMIC_RELEASE);
+  }
+  return 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 JS_DEVICE void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

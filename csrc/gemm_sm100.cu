@@ -839,17 +839,14 @@ template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
                        cudaStream_t stream, int groups = 0, int group_m_tiles = 0) {
   using S = GemmSmem<BN, BUDGET_KB, FP4>;
-  static int configured = 0;
+  static int configured[kMaxDevicesCached] = {};
   auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4>;
   const int recv_total = recv_bytes(split, BN, EPI == EPI_SWIGLU);
   const int data_bytes = recv_aliases_stages(S::kTiles, recv_total) ? (S::kTiles > recv_total ? S::kTiles : recv_total)
                                                                      : S::kTiles + recv_total;
   const int smem_bytes = data_bytes + 1024 /*align slack*/ + 256 /*barriers*/ + ((EPI == EPI_ALLREDUCE || EPI == EPI_EP_COMBINE) ? 8192 + 64 : 0);
   if (smem_bytes > 227 * 1024) return -18;
-  if (smem_bytes > configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -3;
-    configured = smem_bytes;
-  }
+  if (ensure_dyn_smem(kern, smem_bytes, configured) != 0) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
   if (groups > 0) cfg.gridDim = dim3((p.N + BN - 1) / BN, group_m_tiles, groups);   // z = expert, no K split

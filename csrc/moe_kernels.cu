@@ -203,11 +203,8 @@ extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int f
   if (k < 1) return -10;
   if (P > js::kSortMaxPairs || n_local < 1 || E < 1) return -10;
   const int smem = (P + 2 * n_local + 3 + E) * 4;
-  static int configured = 0;
-  if (smem > configured) {
-    if (cudaFuncSetAttribute(js::moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured = smem;
-  }
+  static int configured[js::kMaxDevicesCached] = {};
+  if (js::ensure_dyn_smem(js::moe_sort_kernel, smem, configured) != 0) return -3;
   cudaLaunchConfig_t c = {};
   c.gridDim = dim3(1);
   c.blockDim = dim3(js::kSortThreads);

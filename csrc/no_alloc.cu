@@ -24,16 +24,18 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices] = {};
 
-// Once per device, with that device current.
+// Once per device, with that device current.  Host threads may race to fill a slot: the lookup is
+// idempotent (every thread gets the same address), and the slot is published with release/acquire
+// atomics so no thread ever reads a half-written pointer.
 unsigned char* scratch_for_current_device() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (g_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_scratch) != cudaSuccess) return nullptr;
-    g_scratch_addr[dev] = p;
+  void* p = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_scratch) != cudaSuccess || p == nullptr) return nullptr;
+    __atomic_store_n(&g_scratch_addr[dev], p, __ATOMIC_RELEASE);
   }
-  return static_cast<unsigned char*>(g_scratch_addr[dev]);
+  return static_cast<unsigned char*>(p);
 }
 
 }  // namespace
@@ -54,4 +56,12 @@ extern "C" int js_lm_head_argmax_static(const void* h, const void* w, int M, int
                         nullptr, status, nullptr, 0, stream);
   if (rc != 0) return rc;
   return js_argmax_merge(part_val, part_idx, n_tiles, M, out_idx, out_val, 0, stream);
+}
+
+extern "C" int js_lm_head_argmax_static_status(int* host_status, cudaStream_t stream) {
+  if (host_status == nullptr) return -33;
+  unsigned char* s = scratch_for_current_device();
+  if (s == nullptr) return -31;
+  if (cudaMemcpyAsync(host_status, s + kStatusOffset, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -32;
+  return cudaStreamSynchronize(stream) == cudaSuccess ? 0 : -32;
 }

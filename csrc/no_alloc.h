@@ -34,6 +34,14 @@ extern "C" {
 int js_lm_head_argmax_static(const void* h, const void* w, int M, int N, int K, int lda, int ldw, int* out_idx,
                              float* out_val, cudaStream_t stream);
 
+// The kernels behind js_lm_head_argmax_static never spin forever: a wait that runs out records a code in a
+// status word inside the same scratch array and the call still returns 0 (the launch succeeded), with
+// undefined tokens.  This accessor copies that word to *host_status (0 = the last call on this device ran
+// clean; 1..3 = a bounded wait inside the GEMM gave up) and synchronises `stream`, so call it on the stream
+// the argmax ran on, after it.  Allocates nothing.  Returns 0, -31 (address lookup failed), -32 (copy or
+// synchronisation failed) or -33 (null pointer).
+int js_lm_head_argmax_static_status(int* host_status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

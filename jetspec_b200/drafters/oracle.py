@@ -29,6 +29,8 @@ _BASE_LOGIT = -30.0  # every non-candidate vocabulary entry
 
 
 class OracleTreeDrafter(TreeDrafter):
+    host_scripted = True     # the proposal depends on the context length only: engines may stage it from the host
+
     def __init__(self, continuation: Sequence[int], vocab_size: int, tree_width: int = 7,
                  mean_accept: float = 7.0, max_accept: Optional[int] = None, seed: int = 0,
                  top1_mass: float = 0.9):

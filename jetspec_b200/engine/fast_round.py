@@ -22,7 +22,6 @@ import torch
 
 from ..core.llm import decode_text
 from ..drafters.head import DraftHeadTreeDrafter
-from ..drafters.oracle import OracleOverrideDrafter, OracleTreeDrafter
 from ..models.qwen3 import MLP
 from ..parallel.tp import stack_rows
 from ..ops import cuda_ext as X
@@ -310,11 +309,17 @@ class FastRound:
 
     @staticmethod
     def _split_drafter(drafter):
-        """``(head drafter | None, oracle | None, host drafter | None)``."""
-        if isinstance(drafter, OracleOverrideDrafter):
+        """``(head drafter | None, scripted host drafter | None, other host drafter | None)``.
+
+        Drafter protocol of the graph path (no class checks): a drafter whose proposal needs nothing from the
+        device sets ``host_scripted = True`` (and may offer ``propose_topk_at(context_len, depth, width)``); a
+        wrapper that runs a real drafter for its cost and substitutes a scripted one's candidates exposes them as
+        ``.real`` and ``.oracle``."""
+        scripted = getattr(drafter, "oracle", None)
+        if scripted is not None and hasattr(drafter, "real"):
             real = drafter.real if isinstance(drafter.real, DraftHeadTreeDrafter) else None
-            return real, drafter.oracle, (None if real is not None else drafter.real)
-        if isinstance(drafter, OracleTreeDrafter):
+            return real, scripted, (None if real is not None else drafter.real)
+        if getattr(drafter, "host_scripted", False):
             return None, drafter, None
         if isinstance(drafter, DraftHeadTreeDrafter):
             return drafter, None, None

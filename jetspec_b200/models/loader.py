@@ -36,6 +36,7 @@ def load_state_into(module: torch.nn.Module, path: str, remap: Optional[Callable
     params = dict(module.named_parameters())
     params.update(dict(module.named_buffers()))
     seen = set()
+    seen_slices: dict = {}       # stacked parameter -> set of indices a checkpoint tensor was copied into
     for fn in _checkpoint_files(path):
         with safe_open(fn, framework="pt", device="cpu") as f:
             for key in f.keys():
@@ -50,17 +51,51 @@ def load_state_into(module: torch.nn.Module, path: str, remap: Optional[Callable
                 src = f.get_tensor(key)
                 if index is not None:
                     dst[index].copy_(src.to(dst.dtype))
+                    seen_slices.setdefault(name, set()).add(_index_key(index))
                 else:
                     if tuple(dst.shape) != tuple(src.shape):
                         raise ValueError(f"{key}: checkpoint {tuple(src.shape)} vs model {tuple(dst.shape)}")
                     dst.copy_(src.to(dst.dtype))
                 seen.add(name)
     if strict:
+        # a stacked parameter (per-expert tensors, gate|up halves) counts as loaded only when every slice of it
+        # along the leading axes the remap addresses has been written; otherwise its untouched slices would keep
+        # whatever the allocator left there
+        for name, got in seen_slices.items():
+            want = _expected_slices(params[name], got)
+            if got != want:
+                lost = sorted(want - got)[:4]
+                raise KeyError(f"stacked parameter {name!r} is missing {len(want - got)} of {len(want)} slices "
+                               f"(first: {lost})")
         missing = [n for n, p in module.named_parameters() if n not in seen]
         # a tied lm_head is legitimately absent from the file
         missing = [n for n in missing if n != "lm_head.weight"]
         if missing:
             raise KeyError(f"parameters missing from checkpoint: {missing[:8]}{'…' if len(missing) > 8 else ''}")
+
+
+def _index_key(index) -> tuple:
+    """A hashable form of the index a remap returned (ints and slices along the leading axes)."""
+    if not isinstance(index, tuple):
+        index = (index,)
+    return tuple((i.start, i.stop) if isinstance(i, slice) else int(i) for i in index)
+
+
+def _expected_slices(param, got: set) -> set:
+    """Every index of the form seen in ``got`` that ``param`` has: the leading integer axis runs over its
+    full extent, and a sliced second axis must be covered by the same set of ranges for every leading index."""
+    lead = param.shape[0]
+    tails = {k[1:] for k in got}
+    ranges = sorted(t[0] for t in tails if t and isinstance(t[0], tuple))
+    if ranges:      # the sliced second axis must be tiled completely (gate AND up halves)
+        pos = 0
+        for lo, hi in ranges:
+            if lo > pos:
+                tails.add(((pos, lo),))
+            pos = max(pos, hi)
+        if pos < param.shape[1]:
+            tails.add(((pos, param.shape[1]),))
+    return {(e,) + t for e in range(lead) for t in tails}
 
 
 def save_state(state: dict, path: str, shard_bytes: int = 4 << 30) -> None:

@@ -24,7 +24,8 @@ import torch
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _ROOT = os.path.dirname(_PKG)
-_CSRC = os.path.join(_ROOT, "csrc")
+# kernel sources: inside the installed package (wheel), else beside it (source checkout)
+_CSRC = os.path.join(_PKG, "csrc") if os.path.isdir(os.path.join(_PKG, "csrc")) else os.path.join(_ROOT, "csrc")
 _OUT_DIR = os.path.join(_PKG, "_C")
 LIB_PATH = os.path.join(_OUT_DIR, "libjetspec_sm100.so")
 

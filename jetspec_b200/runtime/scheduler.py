@@ -96,6 +96,10 @@ class Scheduler:
                 break
             before = set(self.cache.resident())
             protect = [r.seq_id for r in out.admitted]
+            if not self._feasible_without(req.seq_id, want, protect):
+                # only the pages of requests admitted in this very step would make room, and those are never
+                # evicted: stop here instead of evicting every other sequence for nothing
+                break
             ok = self._allocate_protecting(req.seq_id, want, protect)
             for sid in before - set(self.cache.resident()):
                 victim = self.running.pop(sid, None)
@@ -117,6 +121,15 @@ class Scheduler:
         out.admission_reason = ("batched" if out.admitted and out.decode_tokens
                                 else "prefill" if out.admitted else "decode")
         return out
+
+    def _feasible_without(self, seq_id: int, want: int, protect: list) -> bool:
+        """Could ``want`` positions be granted by evicting only sequences outside ``protect``?"""
+        cache = self.cache
+        have = len(cache.state(seq_id).pages) if cache.has(seq_id) else 0
+        need = cache.pages_for(want) - have
+        evictable = sum(len(cache.state(sid).pages) for sid in self.running
+                        if sid not in protect and sid != seq_id and cache.has(sid))
+        return need <= cache.free_page_count + evictable
 
     def _allocate_protecting(self, seq_id: int, want: int, protect: list) -> bool:
         """Allocate, evicting policy-chosen victims; never evict a request admitted this step."""

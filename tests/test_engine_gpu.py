@@ -25,6 +25,56 @@ def prompt():
     return torch.randint(0, 4096, (1, 48), generator=torch.Generator().manual_seed(0))
 
 
+@pytest.fixture(scope="module")
+def stable_engine():
+    """A model whose greedy continuation has a wide margin (the next token of ``t`` is ``t + 1``), so every
+    decode path must reproduce it token for token: a wrong mask bit, position or slot shows up as a mismatch."""
+    from jetspec_b200 import JetSpecEngine
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    cfg = Qwen3Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128)
+    model = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.bfloat16, device="cuda", init="stable")
+    return JetSpecEngine(model, device="cuda", dtype=torch.bfloat16, max_seq_len=1024)
+
+
+@pytest.mark.parametrize("budget,depth,width", [(8, 4, 2), (30, 6, 3), (60, 8, 4), (128, 20, 7), (180, 20, 7),
+                                                (250, 24, 8)])
+def test_tree_equals_ar_exactly_on_every_bucket(stable_engine, prompt, budget, depth, width):
+    """Exact gate: tree decoding == the engine's own greedy decode == the counting sequence, on every tree
+    bucket (16 .. 256 nodes) of the graph path."""
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter
+    from jetspec_b200.ops import cuda_ext
+    sp = SamplingParams(0.0, 40)
+    ar = stable_engine.generate(prompt, sp)["token_ids"]
+    expect = [(int(prompt[0, -1]) + 1 + i) % 4096 for i in range(40)]
+    assert ar == expect
+    out = stable_engine.generate_tree(prompt, RandomTreeDrafter(4096, seed=budget), tree_depth=depth, tree_width=width,
+                                      budget=budget, sampling_params=sp, return_stats=True)
+    assert out["token_ids"] == ar
+    # a drafter that proposes the truth: long accepted paths exercise the commit permutation as well
+    from jetspec_b200 import OracleTreeDrafter
+    oracle = OracleTreeDrafter(prompt[0].tolist() + ar, 4096, tree_width=width, mean_accept=4.0,
+                               max_accept=min(depth, (budget - 2) // width + 1), seed=budget)
+    out = stable_engine.generate_tree(prompt, oracle, tree_depth=depth, tree_width=width, budget=budget,
+                                      sampling_params=sp, return_stats=True)
+    assert out["token_ids"] == ar and out["tpf"] > 1.5
+    cuda_ext.check_status("cuda")
+
+
+def test_batched_graph_verify_equals_ar_exactly(stable_engine):
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 4096, (1, n), generator=g) for n in (12, 70, 33)]
+    sp = SamplingParams(0.0, 24)
+    singles = [stable_engine.generate(p, sp)["token_ids"] for p in prompts]
+    for p, s_ in zip(prompts, singles):
+        assert s_ == [(int(p[0, -1]) + 1 + i) % 4096 for i in range(24)]
+    outs = stable_engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=9), block_size=7, tree_width=3,
+                                             budget=24, sampling_params=sp)
+    assert [o["token_ids"] for o in outs] == singles
+    assert [o["token_ids"] for o in stable_engine.generate_batch(prompts, sp)] == singles
+
+
 def teacher_forced_agreement(model, prompt, new_ids):
     """Fraction of generated tokens equal to the argmax of one fp32 causal forward over prompt+output,
     and the worst logit shortfall of a disagreeing token (relative to the row's max |logit|)."""

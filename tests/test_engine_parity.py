@@ -106,3 +106,45 @@ def test_extension_is_lossless(engine, llm, tiny_model, tiny_prompt):
                                extend_kwargs={"gap_threshold": -1e9, "ext_budget": 4})
     assert out["token_ids"] == ref
     assert max(out["accept_lengths"]) > 5     # accepted beyond the un-extended ceiling
+
+
+def test_admission_does_not_evict_for_room_that_only_protected_requests_hold():
+    """A waiting request whose room could only come from requests admitted in the same step must wait: the
+    scheduler stops admitting instead of evicting every other running sequence and failing anyway."""
+    from jetspec_b200.runtime import PagedKVPool, Scheduler, SequenceRequest
+    pool = PagedKVPool(1, 1, 8, num_pages=10, page_size=4, max_seqs=8, max_seq_len=64)
+    sched = Scheduler(pool, max_batch_size=8, prefill_batch_size=8)
+    old = SequenceRequest(seq_id=1, input_ids=list(range(8)), max_new_tokens=4)       # 2 pages, running
+    sched.admit_request(old)
+    out = sched.step()
+    assert [r.seq_id for r in out.admitted] == [1]
+    sched.mark_decode_step(1, 5)
+    # two newcomers: the first takes 6 of the 8 free pages; the second needs 5 and could only fit by also
+    # taking the first newcomer's pages (protected) -- evicting sequence 1 (2 pages) would not be enough
+    sched.admit_request(SequenceRequest(seq_id=2, input_ids=list(range(24)), max_new_tokens=4))
+    sched.admit_request(SequenceRequest(seq_id=3, input_ids=list(range(20)), max_new_tokens=4))
+    out = sched.step()
+    assert [r.seq_id for r in out.admitted] == [2]
+    assert out.evicted == [] and 1 in sched.running and pool.has(1)
+    assert [r.seq_id for r in sched.waiting_queue] == [3]
+
+
+def test_loader_rejects_a_checkpoint_that_lacks_expert_slices(tmp_path):
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    from jetspec_b200.models.loader import save_state
+    cfg = Qwen3Config(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                      num_key_value_heads=1, head_dim=16, num_experts=4, num_experts_per_tok=2,
+                      moe_intermediate_size=16, norm_topk_prob=True, model_type="qwen3_moe")
+    m = Qwen3ForCausalLM.random_init(cfg, seed=0, dtype=torch.float32, device="cpu")
+    m.save_pretrained(str(tmp_path / "full"))
+    again = Qwen3ForCausalLM.from_pretrained(str(tmp_path / "full"), dtype=torch.float32, device="cpu")
+    assert torch.equal(again.model.layers[0].mlp.w_gate_up, m.model.layers[0].mlp.w_gate_up)
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "full" / "model.safetensors"))
+    for drop in ("model.layers.0.mlp.experts.2.up_proj.weight", "model.layers.0.mlp.experts.3.down_proj.weight"):
+        part = {k: v for k, v in sd.items() if k != drop}
+        d = tmp_path / ("lacks_" + drop.split(".")[-2] + drop.split(".")[-3])
+        cfg.save_pretrained(str(d))
+        save_state(part, str(d))
+        with pytest.raises(KeyError, match="missing"):
+            Qwen3ForCausalLM.from_pretrained(str(d), dtype=torch.float32, device="cpu")

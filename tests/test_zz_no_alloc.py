@@ -33,6 +33,9 @@ def test_static_scratch_argmax_matches_allocating_path_twice():
         assert rc == 0, f"call {call}: rc {rc}"
         assert torch.equal(out_idx, ref_idx), f"call {call}: tokens differ"
         assert torch.allclose(out_val, ref_val, rtol=0, atol=8e-3 * float(ref_val.abs().max()))
+        word = ctypes.c_int(-1)                      # the status word of the static path is readable and clean
+        lib.js_lm_head_argmax_static_status.restype = ctypes.c_int
+        assert lib.js_lm_head_argmax_static_status(ctypes.byref(word), stream) == 0 and word.value == 0
     # sizes beyond the built-in scratch are refused, not truncated
     assert fn(p(h), p(w), 129, V, H, h.stride(0), w.stride(0), p(out_idx), p(out_val), stream) == -30
     assert fn(p(h), p(w), 1, 200000, H, h.stride(0), w.stride(0), p(out_idx), p(out_val), stream) == -30
