@@ -7,9 +7,11 @@ seeded weights our own arm uses) together with a minimal word-level tokenizer; p
 passed as token ids.  The engine is then built and driven exactly as the reference's own
 throughput script does (``bench/engine/tps_walltime.py:205-275``): backend
 ``triton_paged_tree_cudagraph_nogather``, fused GEMMs, ``GraphedDraftHead``, ``session=True``.
-The reference's multi-GPU mode is data parallel (every rank a full replica with its own prompts,
-``bench/engine/tps_walltime.py:178-203``): for N > 1 every rank serves its own request from one
-shared scratch checkpoint and the line reports the sum of tokens over the slowest rank's time.
+The reference's multi-GPU mode is data parallel (every rank a full replica,
+``bench/engine/tps_walltime.py:178-203``); it cannot split one request over GPUs.  For N > 1 every
+rank therefore serves a replica of the SAME request from one shared scratch checkpoint, and the
+line reports tokens per second PER REQUEST over the slowest rank's time, the quantity this repo's
+own arm reports when it runs the one request tensor-parallel over the N GPUs.
 
 If any step the reference needs cannot run on this box, the function prints
 ``{"impl": "reference", "unavailable": "<why>"}`` and returns.
@@ -160,7 +162,7 @@ def _run(args, world: int, rank: int, scratch: str) -> dict:
     bs = args.tree_depth + 1
     real = GraphedDraftHead(head, target=eng.model, block_size=bs, target_layer_ids=head.target_layer_ids,
                             draft_shift=False)
-    req_seed = args.seed + (rank if world > 1 else 0)
+    req_seed = args.seed            # every rank serves the same request
     prompt = torch.randint(0, cfg.vocab_size, (1, args.prompt_len),
                            generator=torch.Generator().manual_seed(req_seed)).pin_memory()
     sp = SamplingParams(0.0, args.max_new)
@@ -186,51 +188,61 @@ def _run(args, world: int, rank: int, scratch: str) -> dict:
     torch.cuda.synchronize()
     _sync_ranks(world)
     sampler.start()
-    toks, rounds, accept = 0, 0, []
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    e0.record()
-    for _ in range(args.steps):
+    toks, rounds, accept, dev_ms = 0, 0, [], 0.0
+    oracle.host_seconds = 0.0
+    for _ in range(args.steps):        # one event pair around each whole request, as in this repo's own arm
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         out = eng.generate_tree(prompt, drafter, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        dev_ms += e0.elapsed_time(e1)
         toks += len(out["token_ids"])
         rounds += out["rounds"]
         accept += out["accept_lengths"]
-    e1.record()
+    oracle_s = oracle.host_seconds
+    _sync_ranks(world)
+    t0 = time.perf_counter()
+    e2e_toks = 0
+    for _ in range(args.steps):        # end to end by the wall clock, a second set of steps
+        e2e_toks += len(eng.generate_tree(prompt, drafter, **kw)["token_ids"])
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     return {"toks": toks, "rounds": rounds, "acc_sum": float(sum(accept)), "acc_n": len(accept), "wall": wall,
-            "dev_ms": e0.elapsed_time(e1), "clocks": sampler.stop(), "converged": converged}
+            "e2e_toks": e2e_toks, "dev_ms": dev_ms, "oracle_s": oracle_s, "clocks": sampler.stop(),
+            "converged": converged}
 
 
 def _report(args, allres: list) -> None:
-    from bench import BASELINE_TOK_S
+    from bench import BASELINE_TOK_S, TIMING_NOTE, bench_config
     bad = [r for r in allres if "unavailable" in r]
     if bad:
         return _unavailable(bad[0]["unavailable"])
     n = len(allres)
-    toks, rounds = sum(r["toks"] for r in allres), sum(r["rounds"] for r in allres)
+    r0 = allres[0]                       # every rank served the same request: rank 0's counts, slowest rank's time
     dev_ms, wall = max(r["dev_ms"] for r in allres), max(r["wall"] for r in allres)
-    acc = sum(r["acc_sum"] for r in allres) / max(1, sum(r["acc_n"] for r in allres))
-    value = toks / (dev_ms / 1e3)
+    value = r0["toks"] / (dev_ms / 1e3)
+    rounds = r0["rounds"]
     D, K = args.tree_depth, args.tree_width
     print(json.dumps({
         "metric": "decode tokens/s/request, Qwen3-8B tree budget 128", "value": round(value, 2),
         "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(dev_ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "strong" if n == 1 else "weak",
         "vs_baseline": round(value / BASELINE_TOK_S, 4), "dtype": "bf16", "data": "synthetic",
         "impl": "reference",
-        "config": {"model": f"{args.model} (random init, residual-dominant variant)", "global_batch": n,
-                   "seq_len": args.prompt_len + args.max_new, "parallelism": f"dp{n}",
-                   "tokens_per_s_per_request": round(value / n, 2),
-                   "backend": "triton_paged_tree_cudagraph_nogather + fuse_gemms + GraphedDraftHead + session",
-                   "tree": f"depth {D} width {K} budget {args.budget}",
-                   "mean_tokens_per_round": round(acc, 3),
-                   "ms_per_round": round(dev_ms * n / max(1, rounds), 4),
-                   "oracle_converged": all(r["converged"] for r in allres),
-                   "timing": "CUDA events around whole requests (prefill included), max over ranks",
-                   "l2": "inputs larger than L2 (16 GB of weights per round)"},
-        "clocks": allres[0]["clocks"],
-        "e2e": {"value": round(toks / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": n * args.prompt_len * 8,
+        "config": bench_config(
+            args, n_req=n, parallelism=f"dp{n}" + (" (one replica of the request per GPU; no tensor parallelism exists)" if n > 1 else ""),
+            drafter="1-layer head (5 taps, GraphedDraftHead) + oracle script",
+            backend="triton_paged_tree_cudagraph_nogather + fuse_gemms + GraphedDraftHead + session",
+            mean_tokens=r0["acc_sum"] / max(1, r0["acc_n"]), ms_per_round=None, prefill_ms=None,
+            oracle_ms_per_round=r0["oracle_s"] * 1e3 / max(1, rounds),
+            converged=all(r["converged"] for r in allres), timing=TIMING_NOTE,
+            request_ms_per_round=round(dev_ms / max(1, rounds), 4),
+            decode_only_tokens_per_s=None, aggregate_tokens_per_s=round(value * n, 2)),
+        "clocks": r0["clocks"],
+        "e2e": {"value": round(r0["e2e_toks"] / wall, 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": args.prompt_len * 8 + int(rounds / args.steps * (D * K * 8)),
                 "d2h_bytes_per_step": int(rounds / args.steps * 16)},
         "gpu_launches": 0,
     }), flush=True)

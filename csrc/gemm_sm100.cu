@@ -409,7 +409,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // buffer, sums them in rank order together with the residual and writes the output.  All
       // ranks add the same numbers in the same order, so the replicated result is bit-identical.
       const int fidx = (blockIdx.y * gridDim.x + blockIdx.x) * split + z;
-      if (p.ar_push_only == 2) {
+      if (p.ar_push_only >= 2) {
         // Low-latency push: every pair of bf16 outputs travels in ONE 8-byte store together with a flag word,
         // so the receiver needs no fence, no counter and no extra round trip: it polls the cells themselves
         // (the finishing kernel) and zeroes them after use.  Receive buffer: (world, m_cap, N/2) cells of 8 bytes.
@@ -437,6 +437,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int gr = m0 + prow, pc = gc + part * 8;
             if (gr >= p.M || pc >= p.N) continue;
             const uint4 d = *reinterpret_cast<const uint4*>(stage + prow * 64 + ((part ^ ((prow >> 1) & 3)) << 4));
+            if (p.ar_push_only == 3) {
+              // reduce-scatter form (two-shot all-reduce): columns [o * N/world, (o+1) * N/world) belong to rank o,
+              // which receives only that slice from everybody: (world, m_cap, N/world) cells.  The bytes a rank
+              // sends stay at one partial's worth however many ranks there are.
+              const int nw = p.N / p.world, o = pc / nw;
+              const size_t cell = ((static_cast<size_t>(p.rank) * p.m_cap + gr) * nw + (pc - o * nw)) >> 1;
+              unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_recv[o]) + cell;
+              asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(d.x), "r"(1u), "r"(d.y), "r"(1u) : "memory");
+              asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(d.z), "r"(1u), "r"(d.w), "r"(1u) : "memory");
+              continue;
+            }
             const size_t cell = ((static_cast<size_t>(p.rank) * p.m_cap + gr) * p.N + pc) >> 1;
             for (int r = 0; r < p.world; ++r) {
               unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_recv[r]) + cell;
@@ -925,8 +936,11 @@ extern "C" int js_gemm_bf16_allreduce(const void* A, const void* W, void* C, con
   if (split < 1 || split > 4 || split > kb_total) return -12;
   if (M > m_cap || world < 1 || rank < 0 || rank >= world) return -19;
   const int ctas = ((N + 127) / 128) * ((M + BM - 1) / BM) * split;
-  if (ctas > n_flags) return -20;
-  if (ctas > (split > 1 ? 148 : 2 * 148)) return -21;   // every CTA must be resident: CTAs wait for peers on other GPUs
+  if (push_only < 2) {                                    // the cell modes use neither counters nor waits in the GEMM
+    if (ctas > n_flags) return -20;
+    if (push_only == 0 && ctas > (split > 1 ? 148 : 2 * 148)) return -21;   // CTAs that wait for peers must all be resident
+  }
+  if (push_only == 3 && (N % (8 * world)) != 0) return -23;
   CUtensorMap ta, tw;
   if (make_map(&ta, A, M, K, lda, BM) || make_map(&tw, W, N, K, ldw, 128)) return -16;
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), nullptr, nullptr, nullptr, status,
@@ -1014,8 +1028,11 @@ extern "C" int js_gemm_nvfp4_allreduce(const void* Aq, const void* sfa, const fl
   if (split < 1 || split > 4 || split > K / 256) return -12;
   if (M > m_cap || world < 1 || rank < 0 || rank >= world || !row_scale) return -19;
   const int ctas = ((N + 127) / 128) * ((M + BM - 1) / BM) * split;
-  if (ctas > n_flags) return -20;
-  if (ctas > 148) return -21;           // every CTA must be resident: CTAs wait for peers on other GPUs
+  if (push_only < 2) {
+    if (ctas > n_flags) return -20;
+    if (push_only == 0 && ctas > 148) return -21;           // CTAs that wait for peers must all be resident
+  }
+  if (push_only == 3 && (N % (8 * world)) != 0) return -23;
   CUtensorMap ta, tw;
   if (make_map_u8(&ta, Aq, M, K / 2, lda_bytes, BM) || make_map_u8(&tw, Wq, N, K / 2, ldw_bytes, 128)) return -16;
   GemmParams p{};

@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import math
 import random
+import time
 from typing import Optional, Sequence
 
 import torch
@@ -47,6 +48,8 @@ class OracleTreeDrafter(TreeDrafter):
         self.planned: list = []  # accepted lengths drawn so far (diagnostics)
         self._lp_cache = None
         self._np_cache = None
+        self._logit_buf = None       # (key, persistent (1, D, V) logits, indices scattered by the previous call)
+        self.host_seconds = 0.0      # host time spent producing proposals (benchmarks report it per round)
 
     def set_continuation(self, continuation: Sequence[int]) -> None:
         self.sequence = [int(t) for t in continuation]
@@ -91,19 +94,23 @@ class OracleTreeDrafter(TreeDrafter):
 
     # -- drafter contracts -----------------------------------------------------
     def propose_topk(self, context_ids, depth: int, width: Optional[int] = None, target_hidden=None, **kwargs):
+        t0 = time.perf_counter()
         self.calls += 1
         T = int(context_ids.shape[-1])
         rows = self._candidates(T, depth)
         lp = self._logprobs()
         dev = context_ids.device
-        return (torch.tensor(rows, dtype=torch.long, device=dev),
-                torch.tensor([lp] * depth, dtype=torch.float32, device=dev))
+        out = (torch.tensor(rows, dtype=torch.long, device=dev),
+               torch.tensor([lp] * depth, dtype=torch.float32, device=dev))
+        self.host_seconds += time.perf_counter() - t0
+        return out
 
     def propose_topk_at(self, context_len: int, depth: int, width: Optional[int] = None):
         """The same proposal as :meth:`propose_topk` from the context LENGTH alone (the script depends only on the
         position): ``(tokens (depth, K) int32 array, log-probs (depth, K) list)``.  Engines that stage the top-k on
         the host use this to skip building tensors every round."""
         import numpy as np
+        t0 = time.perf_counter()
         self.calls += 1
         T, V, K = int(context_len), self.vocab_size, self.tree_width
         a = self.planned_accept(T, depth)
@@ -129,17 +136,32 @@ class OracleTreeDrafter(TreeDrafter):
             rows = np.where(lead[:, None], np.concatenate([truth[:, None], fill[:, :K - 1]], axis=1), fill)
         if self._lp_cache is None:
             self._lp_cache = self._logprobs()
-        return rows.astype(np.int32), [self._lp_cache] * depth
+        out = rows.astype(np.int32), [self._lp_cache] * depth
+        self.host_seconds += time.perf_counter() - t0
+        return out
 
     def propose_logits(self, context_ids, depth, target_hidden=None, **kwargs):
+        """Dense ``(1, depth, V)`` logits.  The tensor is a persistent buffer that the NEXT call rewrites (only the
+        candidate entries change between rounds, so a round costs one small upload and two scatters instead of
+        filling ``depth x V`` floats); callers consume it within the round, as every engine here does."""
+        t0 = time.perf_counter()
         self.calls += 1
         T = int(context_ids.shape[-1])
         rows = self._candidates(T, depth)
         dev = context_ids.device
-        logits = torch.full((1, depth, self.vocab_size), _BASE_LOGIT, dtype=torch.float32, device=dev)
+        key = (str(dev), int(depth))
+        if self._logit_buf is None or self._logit_buf[0] != key:
+            vals = torch.tensor(self._cand_logits[: self.tree_width], dtype=torch.float32, device=dev)
+            self._logit_buf = [key, torch.full((1, depth, self.vocab_size), _BASE_LOGIT, dtype=torch.float32, device=dev),
+                               None, vals.expand(depth, -1).contiguous(),
+                               torch.full((depth, self.tree_width), _BASE_LOGIT, dtype=torch.float32, device=dev)]
+        _, logits, prev, vals, base = self._logit_buf
+        if prev is not None:
+            logits[0].scatter_(1, prev, base)
         idx = torch.tensor(rows, dtype=torch.long, device=dev)
-        vals = torch.tensor(self._cand_logits[: self.tree_width], dtype=torch.float32, device=dev)
-        logits[0].scatter_(1, idx, vals.expand(depth, -1).contiguous())
+        logits[0].scatter_(1, idx, vals)
+        self._logit_buf[2] = idx
+        self.host_seconds += time.perf_counter() - t0
         return logits
 
 

@@ -207,6 +207,26 @@ class JetSpecEngine:
         self.pool.state(seq_id).length = T
         return logits, hidden
 
+    def _prefill_batch_member(self, seq_id: int, toks: torch.Tensor, taps, temperature: float):
+        """Prefill one newly admitted request of a batch.  Returns ``(first token, tap hidden | None)``.  Under
+        tensor parallelism the prompt runs through the sharded kernel path (the module forward holds full-size
+        weights and cannot address the sharded KV pool)."""
+        if self.tp is not None and temperature > 0.0:
+            raise NotImplementedError("tensor-parallel batches decode greedily")
+        kernel_path = self.tp is not None
+        if not kernel_path and self.use_kernels and temperature <= 0.0 and self.cfg.head_dim == 128:
+            from .fast_round import FastRound
+            kernel_path = FastRound.get(self)._kernel_prefill_ok()      # the same prompt path as single requests
+        if kernel_path:
+            from .fast_round import FastRound
+            T = int(toks.numel())
+            have = self.pool.state(seq_id).capacity if self.pool.has(seq_id) else 0
+            return FastRound.get(self)._prefill_kernels(seq_id, toks.reshape(1, -1), taps, max(T, have))
+        logits, hidden, _ = self._forward([seq_id], [toks], [0], taps=taps,
+                                          logits_rows=slice(toks.numel() - 1, toks.numel()))
+        self.pool.state(seq_id).length = toks.numel()
+        return int(sample(logits[-1], temperature)), hidden
+
     # ------------------------------------------------------------ AR decode
     @torch.inference_mode()
     def generate(self, prompt, sampling_params: SamplingParams = None) -> dict:
@@ -461,9 +481,8 @@ class JetSpecEngine:
                 sched.restore_sequence(v.seq_id)
             for req in out.admitted:
                 toks = torch.tensor(req.input_ids, device=self.device)
-                logits, _, _ = self._forward([req.seq_id], [toks], [0], logits_rows=slice(toks.numel() - 1, toks.numel()))
-                self.pool.state(req.seq_id).length = toks.numel()
-                self._record_token(sched, req, int(sample(logits[-1], sp.temperature)), results, reqs)
+                first, _ = self._prefill_batch_member(req.seq_id, toks, None, sp.temperature)
+                self._record_token(sched, req, first, results, reqs)
             running = [r for r in sched.running.values() if not r.is_prefill]
             if not running:
                 if not out.admitted and sched.waiting_queue and not sched.running:
@@ -480,7 +499,7 @@ class JetSpecEngine:
             self.last_stats["max_batch"] = max(self.last_stats["max_batch"], len(ready))
             past = [self.pool.state(r.seq_id).length for r in ready]
             if self.use_kernels and sp.temperature <= 0.0 and self.cfg.head_dim == 128 \
-                    and getattr(self, "tp", None) is None and env_flag("JETSPEC_BATCH_GRAPH", True):
+                    and (env_flag("JETSPEC_BATCH_GRAPH", True) or self.tp is not None):
                 # one graph replay per decode step: every sequence contributes a one-node "tree"
                 from .fast_round import FastRound
                 nodes = [_OneNode(r.input_ids[-1]) for r in ready]
@@ -537,8 +556,10 @@ class JetSpecEngine:
         state, reqs = {}, {}
         batch_graph = env_flag("JETSPEC_BATCH_GRAPH", True)     # graph-replayed verify forward for the whole batch
         # when the graph path is certain to take every tree, trees are built as host lists only (no device tensors)
+        if self.tp is not None:
+            batch_graph = True         # the sharded stack exists on the kernel path only
         graph_ok = bool(batch_graph and self.use_kernels and sp.temperature <= 0.0 and self.cfg.head_dim == 128
-                        and getattr(self, "tp", None) is None and n_max <= 256)
+                        and n_max <= 256)
         for i, row in enumerate(id_rows):
             r = SequenceRequest(seq_id=self._new_seq_id(), input_ids=row.tolist(), max_new_tokens=sp.max_new_tokens,
                                 temperature=sp.temperature, use_tree=True, tree_drafter=drafters[i],
@@ -562,10 +583,7 @@ class JetSpecEngine:
                 sched.restore_sequence(v.seq_id)
             for req in out.admitted:
                 toks = torch.tensor(req.input_ids, device=self.device)
-                logits, hidden, _ = self._forward([req.seq_id], [toks], [0], taps=taps,
-                                                  logits_rows=slice(toks.numel() - 1, toks.numel()))
-                self.pool.state(req.seq_id).length = toks.numel()
-                first = int(sample(logits[-1], sp.temperature))
+                first, hidden = self._prefill_batch_member(req.seq_id, toks, taps, sp.temperature)
                 prior = state.get(req.seq_id, {"rounds": 0, "acc": []})
                 state[req.seq_id] = {"committed": torch.cat((toks, torch.tensor([first], device=self.device))),
                                      "hidden": hidden, "rounds": prior["rounds"], "acc": prior["acc"]}
@@ -601,6 +619,9 @@ class JetSpecEngine:
                 from .fast_round import FastRound
                 fast = FastRound.get(self)
                 graph_verify = fast.supports_batch_verify(trees, taps)
+            if self.tp is not None and not graph_verify:
+                raise NotImplementedError("tensor-parallel batches need trees the graph path covers "
+                                          "(greedy, head_dim 128, at most 256 nodes, host-built trees)")
             if graph_verify:
                 # the whole verify forward of all live trees is one graph replay; the logits are never written
                 greedy_seq, hidden = fast.batch_verify([r.seq_id for r in live], trees, past, n_max, taps)

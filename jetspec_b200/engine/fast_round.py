@@ -194,8 +194,12 @@ class WeightPrefetcher:
 
 def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
                    mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True, tp=None, prefetch=None,
-                   then_prefetch=None) -> int:
-    """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count."""
+                   then_prefetch=None, final_norm=None) -> int:
+    """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count.
+
+    ``final_norm = (weight, out)`` also applies the model's last RMSNorm to the stack's output.  Under tensor
+    parallelism every row-parallel GEMM's all-reduce finishes inside the kernel that also computes the NEXT
+    RMSNorm (the following layer's input norm, or ``final_norm``), so a layer launches no separate norm kernels."""
     Hq, Hkv, D, H = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
     scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
     last = len(layers) - 1
@@ -203,6 +207,8 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
     # the split merge is a second launch unless the tcgen05 kernel does it inside a cluster (2 or 4 splits)
     in_kernel = X.attn_impl(Hq, Hkv, 0 if mask_bits is None else mask_bits.shape[1]) == "tc" and st.splits in (2, 4)
     merge_launch = 1 if st.splits > 1 and not in_kernel else 0
+    fuse_norm = tp is not None and tp.push_only >= 2     # the all-reduce tail computes the following norm
+    h_ready = False                                      # st.h already holds this layer's normalised input
     for li, L in enumerate(layers):
         def attend(li=li, L=L):
             X.qkv_post(st.qkv, L["qn"], L["kn"], positions, slots, freq, st.q, k_pools[li], v_pools[li], Hq, Hkv, eps,
@@ -210,6 +216,7 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             X.paged_tree_attention(st.q, k_pools[li], v_pools[li], slot_map, seq_rows, cu_q, past_lens, mask_bits,
                                    scale, causal, st.T, out=st.attn, splits=st.splits, ws=st.attn_ws, pdl=pdl)
         if L.get("fp4"):
+            h_ready = False
             n += _decoder_layer_fp4(cfg, L, st, attend, pdl, tp) + 2 + merge_launch
             if taps is not None and li != last:
                 for j, t in enumerate(tap_ids):
@@ -218,7 +225,10 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
                         n += 1
             continue
         pf = prefetch
-        X.rmsnorm(st.x, L["ln1"], eps, out=st.h, pdl=pdl)
+        if not h_ready:
+            X.rmsnorm(st.x, L["ln1"], eps, out=st.h, pdl=pdl)
+            n += 1
+        h_ready = False
         if pf is not None:
             pf.ahead(L["o"])                   # o_proj's weights arrive while qkv, the KV scatter and attention run
         X.gemm(st.h, L["qkv"], out=st.qkv, pdl=pdl)
@@ -227,13 +237,13 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             pf.ahead(L["gu"])
         if tp is None:
             X.gemm(st.attn, L["o"], out=st.x, residual=st.x, pdl=pdl)
-        else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory
-            tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl)
-        X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
+            X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
+        else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory, finished together with ln2
+            tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl, norm_w=L["ln2"], norm_out=st.h, eps=eps)
         if "moe" in L:
             gate_w, w_gu, w_dn, top_k, renorm = L["moe"]
             st.x.add_(X.moe_forward(st.h, gate_w, w_gu, w_dn, top_k, renorm))
-            n += 6 + merge_launch + 7          # + router GEMM, route, sort, two grouped GEMMs, invert and combine
+            n += 5 + merge_launch + 7          # + router GEMM, route, sort, two grouped GEMMs, invert and combine
             if taps is not None and li != last:
                 for j, t in enumerate(tap_ids):
                     if t == li:
@@ -255,13 +265,22 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
         if tp is None:
             X.gemm(st.act, L["down"], out=st.x, residual=st.x, pdl=pdl)
         else:
-            tp.gemm_allreduce(st.act, L["down"], st.x, residual=st.x, pdl=pdl)
-        n += 8 + merge_launch
+            nw, nout = None, None
+            if fuse_norm and li != last and not layers[li + 1].get("fp4"):
+                nw, nout, h_ready = layers[li + 1]["ln1"], st.h, True
+            elif fuse_norm and li == last and final_norm is not None:
+                nw, nout = final_norm
+                final_norm = None                      # done by the all-reduce tail
+            tp.gemm_allreduce(st.act, L["down"], st.x, residual=st.x, pdl=pdl, norm_w=nw, norm_out=nout, eps=eps)
+        n += 7 + merge_launch + (0 if tp is None else 1 if fuse_norm else 2)
         if taps is not None and li != last:
             for j, t in enumerate(tap_ids):
                 if t == li:
                     X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
                     n += 1
+    if final_norm is not None:
+        X.rmsnorm(st.x, final_norm[0], eps, out=final_norm[1], pdl=pdl)
+        n += 1
     if prefetch is not None:
         prefetch.join()
     return n
@@ -298,7 +317,10 @@ class FastRound:
         self.launches_per_round = 0
         self.timing = False            # when set, each graph replay is bracketed by CUDA events
         self.last_device_ms = 0.0      # summed device time of the last call's rounds
+        self.last_prefill_ms = 0.0     # device time of the last call's prompt phase (target prefill + head context)
+        self._prefill_events: list = []
         self.last_rounds = 0
+        self._tp_graph_key = None
 
     # ------------------------------------------------------------------ support matrix
     def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget) -> bool:
@@ -421,7 +443,7 @@ class FastRound:
         d["cu_q"] = torch.tensor([0, bs], dtype=torch.int32, device=dev)
         d["seq_rows"] = _i32(1, dev)
         d["full_mask"] = torch.full((bs, max(1, (bs + 31) // 32)), -1, dtype=torch.int32, device=dev)
-        nt = X.n_tiles(self.cfg.vocab_size)
+        nt = X.n_tiles(self._draft_lm_head(head).shape[0])
         d["tk_ws"] = {"val": torch.zeros(Dd, nt, 8, dtype=torch.float32, device=dev),
                       "idx": torch.zeros(Dd, nt, 8, dtype=torch.int32, device=dev),
                       "lse": torch.zeros(Dd, nt, 2, dtype=torch.float32, device=dev)}
@@ -429,6 +451,19 @@ class FastRound:
         d["topk_lp"] = torch.zeros(Dd, K, dtype=torch.float32, device=dev)
         d["freq"] = X.inv_freq(hc.head_dim, hc.rope_theta, dev)
         r["draft"] = d
+
+    def _draft_lm_head(self, head) -> torch.Tensor:
+        """The vocabulary matrix the draft head scores against: the target's (its shard under tensor parallelism)."""
+        w = head._fwd.lm_head_w
+        if self.tp is None:
+            return w
+        if w.data_ptr() == self.eng.model.lm_head.weight.data_ptr():
+            return self.lm_head_w
+        key = ("draft_lm_head", id(head))
+        if key not in self.draft_cache:
+            from ..parallel.tp import shard_rows
+            self.draft_cache[key] = shard_rows(w, self.tp.rank, self.tp.world)
+        return self.draft_cache[key]
 
     def _launch_draft(self, r, pdl) -> int:
         head, d = r["head"], r["draft"]
@@ -457,8 +492,12 @@ class FastRound:
                                 None if causal else d["full_mask"], causal, d["freq"], pdl=pdl)
         X.rmsnorm(st.x, hm.norm.weight, eps, out=d["hn"], pdl=pdl)
         rows = d["hn"][:bs - 1] if head.draft_shift else d["hn"][1:bs]
-        X.lm_head_topk_logprobs(rows, head._fwd.lm_head_w, max(1, r["K"]), ws=d["tk_ws"], pdl=pdl,
-                                out_tok=d["topk_tok"], out_lp=d["topk_lp"])
+        if self.tp is None:
+            X.lm_head_topk_logprobs(rows, head._fwd.lm_head_w, max(1, r["K"]), ws=d["tk_ws"], pdl=pdl,
+                                    out_tok=d["topk_tok"], out_lp=d["topk_lp"])
+        else:   # vocabulary-parallel: each rank scores its shard, the per-row records are merged through peer memory
+            self.tp.lm_head_topk_logprobs(rows, self._draft_lm_head(head), self.tp.rank * self.vocab_local,
+                                          max(1, r["K"]), d["tk_ws"], d["topk_tok"], d["topk_lp"], pdl=pdl)
         return n + 3
 
     def _launch_round(self, r, pdl: bool, use_remote: bool = True) -> int:
@@ -494,8 +533,7 @@ class FastRound:
         n += 2 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
                                 r["cu_q"], r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"],
                                 False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp,
-                                prefetch=pf, then_prefetch=self.lm_head_w)
-        X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
+                                prefetch=pf, then_prefetch=self.lm_head_w, final_norm=(self.final_norm, r["xn"]))
         last = cfg.num_hidden_layers - 1
         if r["taps"] is not None:
             for j, t in enumerate(r["tap_ids"]):
@@ -516,12 +554,12 @@ class FastRound:
             remote.target_push_header(r["state"], r["committed"], r["path_idx"], pdl)
             n += 4
         r["result_host"].copy_(r["result"], non_blocking=True)
-        return n + 4
+        return n + 3
 
     # ------------------------------------------------------------------ batched verify (continuous batching)
     def supports_batch_verify(self, trees, tap_ids) -> bool:
         cfg = self.cfg
-        if cfg.head_dim != 128 or self.tp is not None or not trees:
+        if cfg.head_dim != 128 or not trees:
             return False
         return all(t.host is not None and t.num_nodes <= 256 for t in trees)
 
@@ -546,6 +584,9 @@ class FastRound:
         key = ("batch", B, NB, tuple(tap_ids or ()), id(pool))
         r = self.graphs.get(key)
         fresh = r is None
+        if self.tp is not None and B * NB > self.tp.m_cap:
+            raise RuntimeError(f"batched verify of {B} x {NB} rows exceeds the tensor-parallel buffers "
+                               f"(m_cap={self.tp.m_cap}); construct TensorParallel with a larger m_cap")
         if fresh:
             H, T = cfg.hidden_size, B * NB
             n_in = T * (2 + W) + 2 * B
@@ -593,15 +634,27 @@ class FastRound:
             pst[b] = p0
         r["inp"].copy_(r["inp_host"], non_blocking=True)
         if fresh:
+            if self.tp is not None:
+                self.tp.begin_sequence()
             self._launch_batch_verify(r, pdl=False)
             torch.cuda.synchronize()
             X.check_status(dev)
+            if self.tp is not None:
+                self.tp.begin_sequence(self.tp._turn)     # cycle length that is safe across replays
+                r["ring_mod"] = self.tp.ring_mod
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._launch_batch_verify(r, pdl=_PDL)
             r["graph"] = g
             pool.frozen = True
             self.graphs[key] = r
+            self._tp_graph_key = None
+        if self.tp is not None and getattr(self, "_tp_graph_key", None) != key:
+            # the graph's collectives restart their buffer cycle: every rank must have left the previous sequence
+            # of collectives (eager prefill, another graph) before the first replay of this one
+            self.tp.begin_sequence()
+            self.tp.ring_mod = r["ring_mod"]
+            self._tp_graph_key = key
         r["graph"].replay()
         torch.cuda.current_stream().synchronize()
         g_all = r["greedy_host"].numpy().reshape(B, NB)
@@ -617,14 +670,17 @@ class FastRound:
         X.embed(r["tokens"], self.embed_w, out=st.x, pdl=False)
         decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"], r["cu_q"],
                        r["past"], r["positions"], r["slots"], r["mask"], False, self.freq, taps=r["taps"],
-                       tap_ids=r["tap_ids"], pdl=pdl)
-        X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps, out=r["xn"], pdl=pdl)
+                       tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp, final_norm=(self.final_norm, r["xn"]))
         last = cfg.num_hidden_layers - 1
         if r["taps"] is not None:
             for j, t in enumerate(r["tap_ids"]):
                 if t == last:
                     X.gather_rows(r["xn"], None, r["taps"], dst_col0=j * cfg.hidden_size, pdl=pdl)
-        X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        if self.tp is None:
+            X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
+        else:
+            self.tp.lm_head_argmax(r["xn"], self.lm_head_w, self.tp.rank * self.vocab_local, r["am_ws"], r["greedy"],
+                                   r["am_val"], pdl=pdl)
         r["greedy_host"].copy_(r["greedy"], non_blocking=True)
 
     # ------------------------------------------------------------------ sequence setup
@@ -635,11 +691,15 @@ class FastRound:
         remote = r.get("remote")
         if remote is not None:
             remote.reset()
-        if self.tp is None:
+        ev = None
+        if self.timing:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        if self._kernel_prefill_ok():
+            first, hidden = self._prefill_kernels(sid, ids, taps, total)
+        else:
             logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
             first = int(logits[-1].float().argmax())
-        else:
-            first, hidden = self._prefill_kernels(sid, ids, taps, total)
         r["seq_rows"].fill_(pool.state(sid).row)
         state = torch.zeros(8, dtype=torch.int32)
         state[ST_PAST], state[ST_GEN] = T, 1
@@ -649,19 +709,10 @@ class FastRound:
         r["committed"].copy_(committed)
         head = r["head"]
         if head is not None:
-            d, hm = r["draft"], head.head
-            hc = hm.config
-            n = hidden.shape[0]
-            ctx = hm.project_target_hidden(hidden.to(hm.fc.weight.dtype))
-            cos, sin = ref.rope_cos_sin(torch.arange(n, device=self.device), hc.head_dim, hc.rope_theta)
-            for li, layer in enumerate(hm.layers):
-                a = layer.self_attn
-                k = torch.nn.functional.linear(ctx, a.k_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
-                v = torch.nn.functional.linear(ctx, a.v_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
-                k = ref.apply_rope(ref.rmsnorm(k, a.k_norm.weight, hc.rms_norm_eps), cos, sin)
-                d["k"][li][:, :n] = k.transpose(0, 1)
-                d["v"][li][:, :n] = v.transpose(0, 1)
-            state[ST_CTX] = n
+            state[ST_CTX] = self._draft_prompt_context(r, hidden)
+        if ev is not None:
+            ev[1].record()
+            self._prefill_events.append(ev)
         r["state"].copy_(state)
         torch.cuda.synchronize()
         if remote is not None:
@@ -675,6 +726,29 @@ class FastRound:
             self.tp.begin_sequence()      # the graph's collectives restart their buffer cycle here
             self.tp.ring_mod = r.get("ring_mod", self.tp.ring_mod)
         return first
+
+    def _kernel_prefill_ok(self) -> bool:
+        """The prompt runs through the same kernels as the rounds (fused QKV, in-kernel KV scatter, SwiGLU epilogue)
+        whenever the layers are ones :func:`decoder_layers` covers; ``JETSPEC_EAGER_PREFILL=1`` keeps the module path."""
+        return self.tp is not None or os.environ.get("JETSPEC_EAGER_PREFILL", "0") != "1"
+
+    def _draft_prompt_context(self, r, hidden: torch.Tensor) -> int:
+        """Fill the draft head's context K/V for the prompt from the tapped hidden rows, with the same kernels the
+        in-graph context update uses (fc GEMM, RMSNorm, fused K|V GEMM, per-head norm + RoPE + scatter), in row
+        chunks.  Returns the number of context rows."""
+        d, hm = r["draft"], r["head"].head
+        hc = hm.config
+        n, Hkv, eps = hidden.shape[0], hc.num_key_value_heads, hc.rms_norm_eps
+        hid = hidden.to(torch.bfloat16)
+        for s0 in range(0, n, 512):
+            rows = hid[s0:s0 + 512].contiguous()
+            m = rows.shape[0]
+            ctx = X.rmsnorm(X.gemm(rows, hm.fc.weight), hm.hidden_norm.weight, eps)
+            pos = torch.arange(s0, s0 + m, dtype=torch.int32, device=self.device)
+            for li, L in enumerate(d["layers"]):
+                kv = X.gemm(ctx, L["kv"])
+                X.qkv_post(kv, None, L["kn"], pos, pos, d["freq"], None, d["k"][li], d["v"][li], 0, Hkv, eps)
+        return n
 
     def _prefill_kernels(self, sid: int, ids: torch.Tensor, taps, total: int):
         """Causal prefill on the kernel path in chunks (the tensor-parallel route: sharded weights,
@@ -699,9 +773,10 @@ class FastRound:
             past = torch.tensor([s0], dtype=torch.int32, device=dev)
             tapbuf = hidden[s0:s0 + n] if hidden is not None else None
             X.embed(ids32[s0:s0 + n].contiguous(), self.embed_w, out=st.x)
+            xn = torch.empty_like(st.x)
             decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, seq_rows, cu_q, past,
-                           pos, slots, None, True, self.freq, taps=tapbuf, tap_ids=tap_ids, pdl=False, tp=self.tp)
-            xn = X.rmsnorm(st.x, self.final_norm, cfg.rms_norm_eps)
+                           pos, slots, None, True, self.freq, taps=tapbuf, tap_ids=tap_ids, pdl=False, tp=self.tp,
+                           final_norm=(self.final_norm, xn))
             if tap_ids:
                 for j, t in enumerate(tap_ids):
                     if t == last:
@@ -715,6 +790,7 @@ class FastRound:
         else:
             self.tp.lm_head_argmax(h_last, self.lm_head_w, self.tp.rank * self.vocab_local, ws, out_idx)
         pool.state(sid).length = T
+        self._tp_graph_key = None          # eager collectives ran: a batched-verify graph must re-synchronise first
         return int(out_idx.item()), hidden
 
     # ------------------------------------------------------------------ public entry points
@@ -805,6 +881,10 @@ class FastRound:
             torch.cuda.synchronize()
         self.last_rounds = rounds
         self.last_device_ms = float(sum(a.elapsed_time(b) for a, b in events)) if events else 0.0
+        if self._prefill_events:
+            torch.cuda.synchronize()
+            self.last_prefill_ms = float(sum(a.elapsed_time(b) for a, b in self._prefill_events))
+            self._prefill_events = []
         new_ids = new_ids[: sp.max_new_tokens]
         out = {"token_ids": new_ids, "text": decode_text(eng.tokenizer, new_ids),
                "tpf": (len(new_ids) / rounds if rounds else 0.0)}

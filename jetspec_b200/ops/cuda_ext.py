@@ -64,18 +64,40 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 return LIB_PATH
             nvcc = os.environ.get("NVCC", "nvcc")
             tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
-            cmd = [nvcc] + NVCC_FLAGS + ["-I", _CSRC] + sources() + ["-o", tmp]
-            if verbose:
-                cmd.insert(1, "-Xptxas=-v")
-                print(" ".join(cmd), file=sys.stderr)
-            r = subprocess.run(cmd, capture_output=True, text=True)
+            # one object per source, compiled concurrently and kept beside the library, so a change to one
+            # kernel file recompiles that file only; headers invalidate everything
+            obj_dir = os.path.join(_OUT_DIR, "obj")
+            os.makedirs(obj_dir, exist_ok=True)
+            hdr_time = max([os.path.getmtime(f) for f in glob.glob(os.path.join(_CSRC, "*.cuh")) +
+                            glob.glob(os.path.join(_CSRC, "*.h"))] or [0.0])
+            compile_flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas=-v"] if verbose else [])
+            jobs = []
+            for src in sources():
+                obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+                fresh = (not force and os.path.exists(obj)
+                         and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time))
+                jobs.append((src, obj, fresh))
+            procs = [(src, subprocess.Popen([nvcc] + compile_flags + ["-I", _CSRC, "-c", src, "-o", obj],
+                                            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+                     for src, obj, fresh in jobs if not fresh]
+            log = []
+            for src, pr in procs:
+                out, err = pr.communicate()
+                log.append(err)
+                if pr.returncode != 0:
+                    for _, other in procs:
+                        if other.poll() is None:
+                            other.kill()
+                    raise RuntimeError(f"nvcc failed on {os.path.basename(src)}:\n{out}\n{err}")
+            r = subprocess.run([nvcc] + NVCC_FLAGS + [obj for _, obj, _ in jobs] + ["-o", tmp],
+                               capture_output=True, text=True)
             if r.returncode != 0:
                 if os.path.exists(tmp):
                     os.remove(tmp)
-                raise RuntimeError(f"nvcc failed:\n{r.stdout}\n{r.stderr}")
+                raise RuntimeError(f"nvcc link failed:\n{r.stdout}\n{r.stderr}")
             os.replace(tmp, LIB_PATH)
             if verbose:
-                print(r.stderr, file=sys.stderr)
+                print("".join(log), file=sys.stderr)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH

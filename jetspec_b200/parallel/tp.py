@@ -5,11 +5,15 @@ Sharding plan (``world`` ranks, one process per GPU):
 * QKV and gate/up projections are column-parallel (each rank owns ``Hq/world`` query heads,
   ``Hkv/world`` KV heads and ``I/world`` MLP channels, so attention and the KV pool are local);
 * ``o_proj`` and ``down_proj`` are row-parallel: every rank multiplies its K-slice and the
-  partial products are summed by a one-shot all-reduce that is FUSED into the GEMM epilogue —
-  finished tiles are stored into all peers' buffers over NVLink from inside the kernel
-  (``csrc/gemm_sm100.cu``, ``EPI_ALLREDUCE``);
+  partial products are summed by an all-reduce whose first half is FUSED into the GEMM epilogue —
+  finished tiles are stored into peers' buffers over NVLink from inside the kernel
+  (``csrc/gemm_sm100.cu``, ``EPI_ALLREDUCE``) — and whose second half is fused into the NEXT
+  RMSNorm (``csrc/tp_kernels.cu``, ``tp_finish_norm_kernel``), so a tensor-parallel layer launches
+  as many kernels as a single-GPU layer.  Two forms: one shot (every rank receives every
+  partial; 2 ranks) and two shot (reduce-scatter in the GEMM epilogue, all-gather inside the
+  finishing kernel; bytes per rank do not grow with the rank count; 4 and 8 ranks);
 * the LM head is vocabulary-parallel; local (value, token) maxima are combined by a peer-store
-  kernel (``csrc/tp_kernels.cu``);
+  kernel, and so are the draft head's per-shard top-k lists and log-sum-exp (``csrc/tp_kernels.cu``);
 * embeddings, norms and the residual stream are replicated; all ranks add the same numbers in
   the same order, so the replicated state stays bit-identical without further communication.
 
@@ -91,20 +95,36 @@ class TensorParallel:
         self._X = X
         self._turn = 0
         self.ring_mod = 4
-        # push mode (default): the GEMM only pushes its partial tiles and a finishing kernel reduces, so no GEMM CTA
-        # ever waits for a peer; JETSPEC_TP_WAIT_IN_GEMM=1 selects the single-kernel variant that waits in its epilogue
-        #   2 = low-latency cells (8 bytes = two bf16 outputs + a flag word, polled by the finishing kernel: no fence,
-        #       no counter, one NVLink crossing), 1 = bf16 tiles + one release counter per CTA, 0 = wait inside the GEMM
-        mode = os.environ.get("JETSPEC_TP_ALLREDUCE", "ll")
-        self.push_only = {"ll": 2, "flags": 1, "wait": 0}[mode]
+        # all-reduce form (JETSPEC_TP_ALLREDUCE):
+        #   ll   one shot, 8-byte cells {two bf16 outputs, flag word}: no fence, no counter, one NVLink crossing;
+        #        every rank receives every rank's whole partial, so bytes per rank grow with the rank count
+        #   ll2  two shot, same cells: the GEMM epilogue sends each rank only the column slice it owns
+        #        (reduce-scatter), the finishing kernel reduces the slice and stores the result to all ranks
+        #        (all-gather); bytes per rank stay flat
+        #   flags  bf16 tiles + one release counter per CTA, a finishing kernel reduces
+        #   wait   the GEMM CTA waits for its peers in its own epilogue (single kernel)
+        # auto = ll for 2 ranks (one hop less), ll2 beyond.
+        mode = os.environ.get("JETSPEC_TP_ALLREDUCE", "auto")
+        if mode == "auto":
+            mode = "ll" if self.world <= 2 else "ll2"
+        self.mode = mode
+        self.push_only = {"ll": 2, "ll2": 3, "flags": 1, "wait": 0}[mode]
         if os.environ.get("JETSPEC_TP_WAIT_IN_GEMM", "0") == "1":
             self.push_only = 0
         self.recv = [SymmetricBuffer(self.world * self.m_cap * self.n_max * 4, group) for _ in range(self.RING)]
         self.flags = [SymmetricBuffer(self.n_flags * 4, group) for _ in range(self.RING)]
-        self.am_buf = [SymmetricBuffer(self.world * 256 * 8, group) for _ in range(2)]
+        # second-phase (all-gather) cells of the two-shot form: (m_cap, n_max / 2) cells of 8 bytes per buffer
+        self.gather = ([SymmetricBuffer(self.m_cap * self.n_max * 4, group) for _ in range(self.RING)]
+                       if self.push_only == 3 else [])
+        self.am_rows = max(256, min(4096, self.m_cap))
+        self.am_buf = [SymmetricBuffer(self.world * self.am_rows * 8, group) for _ in range(2)]
         self.am_flag = [SymmetricBuffer(64, group) for _ in range(2)]
+        self.tk_rows = 64
+        self.tk_buf = [SymmetricBuffer(self.world * self.tk_rows * 18 * 8, group) for _ in range(2)]
         self._am_turn = 0
+        self._tk_turn = 0
         self.launches = 0
+        self.bytes_pushed = 0          # bytes this rank stored into peers' memory (diagnostic; counted on the host)
 
     @classmethod
     def from_env(cls, **kw) -> "TensorParallel":
@@ -115,53 +135,77 @@ class TensorParallel:
 
     # ---- fused row-parallel GEMM + all-reduce --------------------------------------------------
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                       residual: Optional[torch.Tensor] = None, split: Optional[int] = None, pdl: bool = False):
-        """``out = residual + all_reduce(x @ w.T)`` in ONE kernel per rank.  ``x (M, K/world)``,
-        ``w (N, K/world)``; every rank calls it with the same shapes.  The call order must be the
-        same on all ranks (buffers are taken from a ring by call count)."""
+                       residual: Optional[torch.Tensor] = None, split: Optional[int] = None, pdl: bool = False,
+                       norm_w: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None,
+                       eps: float = 1e-6):
+        """``out = residual + all_reduce(x @ w.T)``; with ``norm_w`` also ``norm_out = rmsnorm(out) * norm_w``
+        from the same finishing kernel.  ``x (M, K/world)``, ``w (N, K/world)``; every rank calls it with the
+        same shapes.  The call order must be the same on all ranks (buffers are taken from a ring by call count)."""
         X = self._X
         lib = X.load()
         M, K = x.shape
         N = w.shape[0]
         assert N <= self.n_max and M <= self.m_cap
-        # Every CTA of a launch waits for its peers on the other GPUs, so a launch must fit the chip in ONE wave:
-        # taller inputs go in row slabs, one launch (and one buffer of the ring) per slab.
         n_tiles = (N + 127) // 128
-        slab = max(1, (2 * X.SM_COUNT) // n_tiles) * 128
-        if M > slab:
-            for m0 in range(0, M, slab):
-                m1 = min(M, m0 + slab)
-                self.gemm_allreduce(x[m0:m1], w, out[m0:m1], None if residual is None else residual[m0:m1], split, pdl)
-            return out
+        if self.push_only == 0:
+            # Every CTA of a launch waits for its peers on the other GPUs, so a launch must fit the chip in ONE
+            # wave: taller inputs go in row slabs, one launch (and one buffer of the ring) per slab.
+            slab = max(1, (2 * X.SM_COUNT) // n_tiles) * 128
+            if M > slab:
+                for m0 in range(0, M, slab):
+                    m1 = min(M, m0 + slab)
+                    self.gemm_allreduce(x[m0:m1], w, out[m0:m1], None if residual is None else residual[m0:m1], split,
+                                        pdl, norm_w, None if norm_out is None else norm_out[m0:m1], eps)
+                return out
         if split is None:
-            tiles = ((N + 127) // 128) * ((M + 127) // 128)
+            tiles = n_tiles * ((M + 127) // 128)
             kb = (K + 63) // 64
             split = 1
             while split < 4 and tiles * (split + 1) <= X.SM_COUNT and kb // (split + 1) >= 2:
                 split += 1
         t = self._turn % self.ring_mod
         self._turn += 1
+        push = self._push_mode(N)
         rc = lib.js_gemm_bf16_allreduce(X._p(x), X._p(w), X._p(out), X._p(residual), M, N, K, x.stride(0), w.stride(0),
                                         out.stride(0), split, X._p(self.recv[t].ptrs_dev), X._p(self.flags[t].ptrs_dev),
                                         self.rank, self.world, self.m_cap, self.n_flags,
-                                        X._p(X.status_word(x.device)), int(pdl), int(self.push_only), X._stream())
-        X._check(rc, f"js_gemm_bf16_allreduce(M={M},N={N},K={K},split={split})")
+                                        X._p(X.status_word(x.device)), int(pdl), push, X._stream())
+        X._check(rc, f"js_gemm_bf16_allreduce(M={M},N={N},K={K},split={split},mode={push})")
         self.launches += 1
-        if self.push_only:
-            self._finish(t, out, residual, M, N, split, pdl)
+        if push:
+            self._finish(t, out, residual, M, N, split, pdl, push, norm_w, norm_out, eps)
+        elif norm_w is not None:
+            X.rmsnorm(out, norm_w, eps, out=norm_out, pdl=pdl)
+            self.launches += 1
         return out
 
-    def _finish(self, t: int, out, residual, M: int, N: int, split: int, pdl: bool) -> None:
-        """Second kernel of the push-mode all-reduce: wait for every rank's tiles, sum in rank order, add the residual."""
+    def _push_mode(self, N: int) -> int:
+        """The epilogue mode of this call: the two-shot form needs the columns to split evenly over the ranks."""
+        if self.push_only == 3 and N % (8 * self.world):
+            return 2
+        return int(self.push_only)
+
+    def _finish(self, t: int, out, residual, M: int, N: int, split: int, pdl: bool, push: int,
+                norm_w=None, norm_out=None, eps: float = 1e-6) -> None:
+        """Second kernel of the push-mode all-reduce: wait for every rank's tiles, sum in rank order, add the
+        residual (and, in the cell modes, apply the following RMSNorm in the same pass)."""
         X = self._X
         lib = X.load()
-        if self.push_only == 2:
-            lib.js_tp_allreduce_finish_ll.restype = ctypes.c_int
-            rc = lib.js_tp_allreduce_finish_ll(ctypes.c_void_p(self.recv[t].local), X._p(residual), X._p(out), M, N,
-                                               out.stride(0), self.m_cap, self.world, X._p(X.status_word(out.device)),
-                                               int(pdl), X._stream())
-            X._check(rc, "js_tp_allreduce_finish_ll")
+        if push >= 2:
+            lib.js_tp_finish_norm.restype = ctypes.c_int
+            two = push == 3
+            rc = lib.js_tp_finish_norm(ctypes.c_void_p(self.recv[t].local),
+                                       X._p(self.gather[t].ptrs_dev) if two else ctypes.c_void_p(0),
+                                       X._p(residual), X._p(out), out.stride(0), X._p(norm_w), X._p(norm_out),
+                                       norm_out.stride(0) if norm_out is not None else 0, ctypes.c_float(eps), M, N,
+                                       self.m_cap, self.world, self.rank, int(two), X._p(X.status_word(out.device)),
+                                       int(pdl), X._stream())
+            X._check(rc, "js_tp_finish_norm")
             self.launches += 1
+            # cells are 8 bytes per two bf16 values: one shot sends the whole partial to every peer, two shot one
+            # slice per peer in each of the two phases
+            per_peer = M * N * 4
+            self.bytes_pushed += (self.world - 1) * (2 * per_peer // self.world if two else per_peer)
             return
         lib.js_tp_allreduce_finish.restype = ctypes.c_int
         rc = lib.js_tp_allreduce_finish(ctypes.c_void_p(self.recv[t].local), ctypes.c_void_p(self.flags[t].local),
@@ -169,6 +213,10 @@ class TensorParallel:
                                         X._p(X.status_word(out.device)), int(pdl), X._stream())
         X._check(rc, "js_tp_allreduce_finish")
         self.launches += 1
+        self.bytes_pushed += (self.world - 1) * M * N * 2
+        if norm_w is not None:
+            X.rmsnorm(out, norm_w, eps, out=norm_out, pdl=pdl)
+            self.launches += 1
 
     def gemm_allreduce_nvfp4(self, act: dict, qw, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                              split: Optional[int] = None, pdl: bool = False):
@@ -189,6 +237,7 @@ class TensorParallel:
                 split += 1
         t = self._turn % self.ring_mod
         self._turn += 1
+        push = self._push_mode(N)
         lib.js_gemm_nvfp4_allreduce.restype = ctypes.c_int
         rc = lib.js_gemm_nvfp4_allreduce(X._p(act["packed"]), X._p(act["sf"]), X._p(act["outer"]), X._p(qw.packed),
                                          X._p(qw.scales_swizzled), ctypes.c_float(qw._w_scale), X._p(out),
@@ -196,11 +245,11 @@ class TensorParallel:
                                          out.stride(0), split, X._p(self.recv[t].ptrs_dev),
                                          X._p(self.flags[t].ptrs_dev), self.rank, self.world, self.m_cap,
                                          self.n_flags, X._p(X.status_word(out.device)), int(pdl),
-                                         int(self.push_only), X._stream())
+                                         push, X._stream())
         X._check(rc, f"js_gemm_nvfp4_allreduce(M={M},N={N},K={K},split={split})")
         self.launches += 1
-        if self.push_only:
-            self._finish(t, out, residual, M, N, split, pdl)
+        if push:
+            self._finish(t, out, residual, M, N, split, pdl, push)
         return out
 
     def begin_sequence(self, calls_per_replay: Optional[int] = None) -> None:
@@ -212,6 +261,7 @@ class TensorParallel:
         dist.barrier(group=self.group)
         self._turn = 0
         self._am_turn = 0
+        self._tk_turn = 0
         if calls_per_replay is not None:
             self.ring_mod = next(r for r in (4, 5, 3, 6) if calls_per_replay % r not in (1, 2))
 
@@ -231,19 +281,52 @@ class TensorParallel:
         X = self._X
         lib = X.load()
         M = h.shape[0]
-        assert M <= 256
+        assert M <= self.am_rows
         nt = X.n_tiles(w_local.shape[0])
         X.gemm(h, w_local, out=None, epi=X.EPI_ARGMAX, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"])
         t = self._am_turn % 2
         self._am_turn += 1
         rc = lib.js_tp_argmax_combine(X._p(ws["val"]), X._p(ws["idx"]), nt, M, int(vocab_offset),
                                       X._p(self.am_buf[t].ptrs_dev), X._p(self.am_flag[t].ptrs_dev), self.rank,
-                                      self.world, 256, X._p(out_idx), X._p(out_val), X._p(X.status_word(h.device)),
+                                      self.world, self.am_rows, X._p(out_idx), X._p(out_val), X._p(X.status_word(h.device)),
                                       int(pdl), X._stream())
         X._check(rc, "js_tp_argmax_combine")
         self.launches += 2
         return out_idx
 
+    def lm_head_topk_logprobs(self, h: torch.Tensor, w_local: torch.Tensor, vocab_offset: int, k: int, ws: dict,
+                              out_tok: torch.Tensor, out_lp: torch.Tensor, pdl: bool = False):
+        """Vocabulary-parallel top-``k`` tokens with full-vocabulary log-probabilities (the draft head's logits):
+        the top-k GEMM epilogue over this rank's shard, then one kernel that merges the local tiles, exchanges the
+        per-row records through peer memory and merges them identically on every rank."""
+        X = self._X
+        lib = X.load()
+        M = h.shape[0]
+        assert M <= self.tk_rows and 1 <= k <= 8
+        nt = X.n_tiles(w_local.shape[0])
+        X.gemm(h, w_local, out=None, epi=X.EPI_TOPK, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"],
+               part_lse=ws["lse"])
+        t = self._tk_turn % 2
+        self._tk_turn += 1
+        lib.js_tp_topk_combine.restype = ctypes.c_int
+        rc = lib.js_tp_topk_combine(X._p(ws["val"]), X._p(ws["idx"]), X._p(ws["lse"]), nt, M, int(k), int(vocab_offset),
+                                    X._p(self.tk_buf[t].ptrs_dev), self.rank, self.world, self.tk_rows, X._p(out_tok),
+                                    X._p(out_lp), X._p(X.status_word(h.device)), int(pdl), X._stream())
+        X._check(rc, "js_tp_topk_combine")
+        self.launches += 2
+        return out_tok, out_lp
+
+    def reset_buffers(self) -> None:
+        """Zero this rank's receive cells and counters (all ranks together): only needed after a call reported a
+        peer timeout, which can leave unconsumed cells behind."""
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for b in self.recv + self.flags + self.gather + self.am_buf + self.am_flag + self.tk_buf:
+            b.zero_local()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
     def close(self):
-        for b in self.recv + self.flags + self.am_buf + self.am_flag:
+        for b in self.recv + self.flags + self.gather + self.am_buf + self.am_flag + self.tk_buf:
             b.close()

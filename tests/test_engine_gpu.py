@@ -61,7 +61,7 @@ def test_tree_equals_ar_exactly_on_every_bucket(stable_engine, prompt, budget, d
     cuda_ext.check_status("cuda")
 
 
-def test_batched_graph_verify_equals_ar_exactly(stable_engine):
+def test_batched_graph_verify_equals_ar_exactly(stable_engine, monkeypatch):
     from jetspec_b200 import SamplingParams, RandomTreeDrafter
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, 4096, (1, n), generator=g) for n in (12, 70, 33)]
@@ -73,6 +73,10 @@ def test_batched_graph_verify_equals_ar_exactly(stable_engine):
                                              budget=24, sampling_params=sp)
     assert [o["token_ids"] for o in outs] == singles
     assert [o["token_ids"] for o in stable_engine.generate_batch(prompts, sp)] == singles
+    monkeypatch.setenv("JETSPEC_BATCH_GRAPH", "0")          # the eager ragged forward must agree token for token too
+    eouts = stable_engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=9), block_size=7, tree_width=3,
+                                              budget=24, sampling_params=sp)
+    assert [o["token_ids"] for o in eouts] == singles
 
 
 def teacher_forced_agreement(model, prompt, new_ids):
@@ -234,6 +238,10 @@ def test_batched_graph_verify_is_lossless_and_matches_the_eager_batch(engine, sm
     assert [o["token_ids"] for o in houts] == singles
     monkeypatch.setenv("JETSPEC_BATCH_GRAPH", "0")
     eouts = engine.generate_tree_batch(prompts, RandomTreeDrafter(4096, seed=7), **kw)
-    agree = sum(a == b for o, s in zip(eouts, singles) for a, b in zip(o["token_ids"], s)) / (20 * len(prompts))
-    assert agree > 0.9            # a different forward (separate projections): bf16 near-ties may flip late tokens
+    # a different forward (separate projections): on this near-tie model a flipped bf16 tie changes everything after
+    # it, so the eager batch is judged against an fp32 teacher-forced pass over ITS OWN tokens (the exact comparison
+    # of the two batch paths runs on the wide-margin model, test_batched_graph_verify_equals_ar_exactly)
+    for p, o in zip(prompts, eouts):
+        agree, short = teacher_forced_agreement(small, p, o["token_ids"])
+        assert agree > 0.85 and short < 0.05
     cuda_ext.check_status("cuda")

@@ -10,8 +10,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(nproc: int, *args, timeout=600):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _launch(nproc: int, *args, timeout=600, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "tp_worker.py"), *args]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
@@ -20,6 +20,12 @@ def _launch(nproc: int, *args, timeout=600):
 
 def test_fused_collectives_two_ranks():
     rc, out = _launch(2)
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+def test_two_shot_allreduce_two_ranks():
+    """The reduce-scatter + all-gather form (the default beyond 2 ranks), forced on at 2 ranks, engine included."""
+    rc, out = _launch(2, "engine", JETSPEC_TP_ALLREDUCE="ll2")
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
 
 
@@ -36,4 +42,10 @@ def test_disaggregated_draft_head_two_ranks():
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_tp_engine_four_ranks():
     rc, out = _launch(4, "engine")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_tp_engine_eight_ranks():
+    rc, out = _launch(8, "engine", timeout=900)
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]

@@ -78,14 +78,28 @@ def main():
             torch.cuda.synchronize()
         ref = x.float() @ w.float().t() + res.float()
         err = float((out.float() - ref).abs().max() / ref.abs().max())
+        # the same all-reduce with the FOLLOWING RMSNorm computed by its finishing kernel
+        nw = (1.0 + 0.1 * torch.randn(N, generator=g, device="cuda")).to(torch.bfloat16)
+        out2, h2 = res.clone(), torch.empty_like(res)
+        for rep in range(3):
+            out2.copy_(res)
+            tp.gemm_allreduce(xl, wl, out2, residual=out2, norm_w=nw, norm_out=h2, eps=1e-6)
+            torch.cuda.synchronize()
+        o32 = out2.float()
+        h_ref = o32 * torch.rsqrt(o32.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+        err_n = float((h2.float() - h_ref).abs().max() / h_ref.abs().max())
+        same_x = torch.equal(out2, out)
         base = torch.empty_like(res)
         tp.gemm_allreduce_nccl(xl, wl, base, residual=res)
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)
         same = all(torch.equal(gathered[0], t) for t in gathered)      # replicas must be bit-identical
+        dist.all_gather(gathered, h2)
+        same &= all(torch.equal(gathered[0], t) for t in gathered)
         if rank == 0:
-            print(f"gemm_allreduce M={M} N={N} K={K}: rel err {err:.2e}, replicas identical {same}", flush=True)
-        ok &= err < 1.5e-2 and same
+            print(f"gemm_allreduce[{tp.mode}] M={M} N={N} K={K}: rel err {err:.2e}, fused norm err {err_n:.2e}, "
+                  f"same residual {same_x}, replicas identical {same}", flush=True)
+        ok &= err < 1.5e-2 and err_n < 1.5e-2 and same and same_x
     # vocabulary-parallel argmax
     M, V, H = 128, 8192, 512
     h = torch.randn(M, H, generator=g, device="cuda").to(torch.bfloat16)
@@ -103,6 +117,28 @@ def main():
     if rank == 0:
         print(f"tp argmax: worst shortfall {gap:.3e}", flush=True)
     ok &= gap < 0.05
+    # vocabulary-parallel top-k with full-vocabulary log-probabilities (the draft head's logits)
+    Mt, Kt = 20, 7
+    ht = h[:Mt].contiguous()
+    tk_ws = {"val": torch.empty(Mt, nt, 8, dtype=torch.float32, device="cuda"),
+             "idx": torch.empty(Mt, nt, 8, dtype=torch.int32, device="cuda"),
+             "lse": torch.empty(Mt, nt, 2, dtype=torch.float32, device="cuda")}
+    o_tok = torch.empty(Mt, Kt, dtype=torch.int32, device="cuda")
+    o_lp = torch.empty(Mt, Kt, dtype=torch.float32, device="cuda")
+    for _ in range(3):
+        tp.lm_head_topk_logprobs(ht, wl, rank * (V // world), Kt, tk_ws, o_tok, o_lp)
+        torch.cuda.synchronize()
+    lsm = torch.log_softmax(logits[:Mt], -1)
+    ref_lp, ref_tok = lsm.topk(Kt, -1)
+    lp_err = float((o_lp - lsm.gather(1, o_tok.long())).abs().max())          # the reported log-prob is the token's own
+    short = float((ref_lp - o_lp).abs().max())                                 # and the k-th best is as good as the true one
+    gathered = [torch.empty_like(o_tok) for _ in range(world)]
+    dist.all_gather(gathered, o_tok)
+    same_t = all(torch.equal(gathered[0], t) for t in gathered)
+    if rank == 0:
+        print(f"tp top-k: log-prob err {lp_err:.3e}, shortfall vs exact top-k {short:.3e}, replicas identical {same_t}",
+              flush=True)
+    ok &= lp_err < 2e-2 and short < 2e-2 and same_t
     ok &= ep_check(rank, world)
     ok &= nvfp4_check(tp, rank, world)
     X.check_status("cuda")
@@ -201,6 +237,28 @@ def engine_check(tp, rank, world, nvfp4: bool = False) -> bool:
     good = ar == expect and out["token_ids"] == expect and out["tpf"] > 2.0
     if rank == 0:
         print(f"tp engine{' (nvfp4)' if nvfp4 else ''}: AR ok {ar == expect}, tree ok {out['token_ids'] == expect}, tokens/round {out['tpf']:.2f}", flush=True)
+    if not nvfp4:
+        # a real draft head inside the round graph (vocabulary-parallel top-k) and continuous batching through the
+        # sharded stack: every request must reproduce the counting sequence
+        from jetspec_b200 import DraftHeadTreeDrafter, RandomTreeDrafter
+        from jetspec_b200.models import DraftHeadModel, draft_head_config
+        hcfg = draft_head_config(cfg, num_layers=1, block_size=9, num_taps=3)
+        head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+        hout = eng.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=9), tree_depth=8, tree_width=4,
+                                 budget=32, sampling_params=sp, return_stats=True)
+        good &= hout["token_ids"] == expect
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, cfg.vocab_size, (1, n), generator=g) for n in (17, 40, 9)]
+        sp2 = SamplingParams(0.0, 20)
+        want = [[(int(p[0, -1]) + 1 + i) % cfg.vocab_size for i in range(20)] for p in prompts]
+        bouts = eng.generate_tree_batch(prompts, RandomTreeDrafter(cfg.vocab_size, seed=7), block_size=5, tree_width=3,
+                                        budget=16, sampling_params=sp2)
+        b_ok = [o["token_ids"] for o in bouts] == want
+        a_ok = [o["token_ids"] for o in eng.generate_batch(prompts, sp2)] == want
+        if rank == 0:
+            print(f"tp engine: in-graph head ok {hout['token_ids'] == expect}, tree batch ok {b_ok}, AR batch ok {a_ok}",
+                  flush=True)
+        good &= b_ok and a_ok
     return good
 
 
