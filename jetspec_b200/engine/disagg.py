@@ -56,7 +56,7 @@ class DraftWorker:
                                             lm_head=types.SimpleNamespace(weight=lm_head_w))
         self.drafter = DraftHeadTreeDrafter(head_model, stub_target, block_size=channel.depth + 1, draft_shift=draft_shift)
         fr = FastRound.__new__(FastRound)
-        fr.device, fr.draft_cache = torch.device(dev), {}
+        fr.device, fr.draft_cache, fr.tp = torch.device(dev), {}, None
         fr.cfg = types.SimpleNamespace(vocab_size=vocab_size)
         fr.eng = types.SimpleNamespace(pool=types.SimpleNamespace(max_seq_len=max_ctx))
         self.fr = fr
@@ -82,18 +82,7 @@ class DraftWorker:
     @torch.inference_mode()
     def load_context(self, hidden: torch.Tensor) -> None:
         """Project the prompt's tapped hidden rows into the head's context K/V (once per request)."""
-        d, hm = self.r["draft"], self.drafter.head
-        hc = hm.config
-        n = hidden.shape[0]
-        ctx = hm.project_target_hidden(hidden.to(hm.fc.weight.dtype))
-        cos, sin = ref.rope_cos_sin(torch.arange(n, device=hidden.device), hc.head_dim, hc.rope_theta)
-        for li, layer in enumerate(hm.layers):
-            a = layer.self_attn
-            k = torch.nn.functional.linear(ctx, a.k_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
-            v = torch.nn.functional.linear(ctx, a.v_proj.weight).view(n, hc.num_key_value_heads, hc.head_dim)
-            k = ref.apply_rope(ref.rmsnorm(k, a.k_norm.weight, hc.rms_norm_eps), cos, sin)
-            d["k"][li][:, :n] = k.transpose(0, 1)
-            d["v"][li][:, :n] = v.transpose(0, 1)
+        n = self.fr._draft_prompt_context(self.r, hidden)     # the same kernels as the in-graph context update
         st = torch.zeros(8, dtype=torch.int32)
         st[ST_CTX] = n
         self.r["state"].copy_(st)

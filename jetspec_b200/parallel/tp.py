@@ -9,9 +9,9 @@ Sharding plan (``world`` ranks, one process per GPU):
   finished tiles are stored into peers' buffers over NVLink from inside the kernel
   (``csrc/gemm_sm100.cu``, ``EPI_ALLREDUCE``) — and whose second half is fused into the NEXT
   RMSNorm (``csrc/tp_kernels.cu``, ``tp_finish_norm_kernel``), so a tensor-parallel layer launches
-  as many kernels as a single-GPU layer.  Two forms: one shot (every rank receives every
-  partial; 2 ranks) and two shot (reduce-scatter in the GEMM epilogue, all-gather inside the
-  finishing kernel; bytes per rank do not grow with the rank count; 4 and 8 ranks);
+  as many kernels as a single-GPU layer.  Two forms: two shot (default: reduce-scatter in the GEMM
+  epilogue, all-gather inside the finishing kernel; bytes per rank do not grow with the rank
+  count) and one shot (every rank receives every partial);
 * the LM head is vocabulary-parallel; local (value, token) maxima are combined by a peer-store
   kernel, and so are the draft head's per-shard top-k lists and log-sum-exp (``csrc/tp_kernels.cu``);
 * embeddings, norms and the residual stream are replicated; all ranks add the same numbers in
@@ -103,10 +103,11 @@ class TensorParallel:
         #        (all-gather); bytes per rank stay flat
         #   flags  bf16 tiles + one release counter per CTA, a finishing kernel reduces
         #   wait   the GEMM CTA waits for its peers in its own epilogue (single kernel)
-        # auto = ll for 2 ranks (one hop less), ll2 beyond.
+        # auto = ll2: measured faster than ll already at 2 ranks (Qwen3-8B round 4.60 against 4.66 ms: half the
+        # bytes per phase outweigh the extra hop), and the only form whose traffic does not grow with the world.
         mode = os.environ.get("JETSPEC_TP_ALLREDUCE", "auto")
         if mode == "auto":
-            mode = "ll" if self.world <= 2 else "ll2"
+            mode = "ll2"
         self.mode = mode
         self.push_only = {"ll": 2, "ll2": 3, "flags": 1, "wait": 0}[mode]
         if os.environ.get("JETSPEC_TP_WAIT_IN_GEMM", "0") == "1":

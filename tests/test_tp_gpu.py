@@ -23,9 +23,9 @@ def test_fused_collectives_two_ranks():
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
 
 
-def test_two_shot_allreduce_two_ranks():
-    """The reduce-scatter + all-gather form (the default beyond 2 ranks), forced on at 2 ranks, engine included."""
-    rc, out = _launch(2, "engine", JETSPEC_TP_ALLREDUCE="ll2")
+def test_one_shot_allreduce_two_ranks():
+    """The one-shot form (every rank receives every partial; the default is the two-shot form), engine included."""
+    rc, out = _launch(2, "engine", JETSPEC_TP_ALLREDUCE="ll")
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
 
 

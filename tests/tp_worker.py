@@ -144,7 +144,8 @@ def main():
     X.check_status("cuda")
     if len(sys.argv) > 1 and sys.argv[1] == "engine":
         ok &= engine_check(tp, rank, world)
-        ok &= engine_check(tp, rank, world, nvfp4=True)
+        if (1024 // world) % 256 == 0:          # the 4-bit GEMM wants K-slices that are multiples of 256
+            ok &= engine_check(tp, rank, world, nvfp4=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
