@@ -4,8 +4,10 @@ conditioned-vs-marginal drafter probe.
 Counterparts of the reference's ``bench/profiling/*.py``.  Everything that computes a statistic is a
 pure function (unit-tested on CPU); the ``main`` at the bottom runs them on a model:
 
-    python bench/profiling.py diagnostics   [--model DIR] [--head DIR]
-    python bench/profiling.py depth-rank    --out profile.json
+    python bench/profiling.py diagnostics      [--model DIR] [--head DIR]
+    python bench/profiling.py depth-rank       --out profile.json     # engine path, accepted chain only
+    python bench/profiling.py llm-depth-rank   --out profile.json     # reference-engine path, every tree node
+    python bench/profiling.py conditioned-probe                       # does path conditioning help the drafter?
     python bench/profiling.py verify-split
 """
 from __future__ import annotations
@@ -152,6 +154,58 @@ def depth_rank_profile(hits, trials, meta: Optional[dict] = None) -> dict:
     return {"depth_rank_accept": table, "meta": dict(meta or {}, trials=list(trials))}
 
 
+def all_node_rank_counts(depths: Sequence[int], target_pick: Sequence[int], topk_tokens: Sequence[Sequence[int]],
+                         hits=None, totals=None):
+    """Every node of a verified tree at depth ``d < D`` is a parent the drafter offered ``K`` children to
+    (its depth-``d`` top-k); count the rank of the token the TARGET picked there.  ``hits[d][r]`` / ``totals[d]``
+    = P(target pick at a depth-``d`` parent is the drafter's rank ``r``): the table ``depth_rank_histogram`` reads
+    (reference collector: ``bench/profiling/collect_depth_rank_stats.py:32-101``, which counts the same event)."""
+    D = len(topk_tokens)
+    K = len(topk_tokens[0]) if D else 0
+    hits = hits if hits is not None else [[0] * K for _ in range(D)]
+    totals = totals if totals is not None else [0] * D
+    rank = [{int(t): r for r, t in enumerate(row)} for row in topk_tokens]
+    for d, pick in zip(depths, target_pick):
+        if d >= D:
+            continue
+        totals[d] += 1
+        r = rank[d].get(int(pick))
+        if r is not None:
+            hits[d][r] += 1
+    return hits, totals
+
+
+class LLMRoundCollector:
+    """``on_round`` hook for :meth:`jetspec_b200.LLM.generate_tree`: per-node depth-rank counts and, when the
+    drafter can condition on a path, the conditioned-vs-marginal rank of every correction token."""
+
+    def __init__(self, width: int, depth: int, drafter=None, probe: bool = False):
+        self.width, self.depth, self.drafter, self.probe = int(width), int(depth), drafter, bool(probe)
+        self.hits = [[0] * self.width for _ in range(self.depth)]
+        self.totals = [0] * self.depth
+        self.marginal_ranks: list = []
+        self.conditioned_ranks: list = []
+
+    def __call__(self, info: dict) -> None:
+        lp = torch.log_softmax(info["draft_logits"][0].float(), -1)
+        top = torch.topk(lp, self.width, dim=-1).indices.tolist()
+        tree = info["tree"]
+        all_node_rank_counts(tree.depth.tolist(), info["target_argmax"].tolist(), top, self.hits, self.totals)
+        acc = info["accepted"]
+        if not self.probe or acc >= lp.shape[0] or acc == 0:
+            return           # nothing was accepted, or the whole chain was: no failed depth to look at
+        cond_fn = getattr(self.drafter, "propose_logits_conditioned", None)
+        if cond_fn is None:
+            return
+        path_tokens = tree.token_ids[info["path"][1:]]
+        cond = cond_fn(info["committed"], path_tokens, target_hidden=info["target_hidden"])
+        self.marginal_ranks.append(rank_of(info["correction"], lp[acc]))
+        self.conditioned_ranks.append(rank_of(info["correction"], cond[0, acc].float()))
+
+    def profile(self, meta: Optional[dict] = None) -> dict:
+        return depth_rank_profile(self.hits, self.totals, meta)
+
+
 # ----------------------------------------------------------------------------- conditioned vs marginal probe
 def rank_of(token: int, logits_row: torch.Tensor) -> int:
     """0-based rank of ``token`` in a logits row."""
@@ -194,7 +248,7 @@ def _setup(args):
 def main():
     from jetspec_b200 import SamplingParams
     ap = argparse.ArgumentParser()
-    ap.add_argument("mode", choices=["diagnostics", "depth-rank", "verify-split"])
+    ap.add_argument("mode", choices=["diagnostics", "depth-rank", "llm-depth-rank", "conditioned-probe", "verify-split"])
     ap.add_argument("--model", default=None)
     ap.add_argument("--head", default=None)
     ap.add_argument("--depth", type=int, default=4)
@@ -234,6 +288,23 @@ def main():
         if args.out:
             open(args.out, "w").write(text)
         print(text)
+    elif args.mode in ("llm-depth-rank", "conditioned-probe"):
+        # the reference-engine path (full tree in one masked forward): the hook sees every node of every round
+        from jetspec_b200 import LLM
+        llm = LLM(eng.model, device=eng.device, dtype=eng.dtype, tokenizer=eng.tokenizer)
+        col = LLMRoundCollector(args.width, args.depth, drafter, probe=args.mode == "conditioned-probe")
+        for p in prompts:
+            llm.generate_tree(p, drafter, block_size=args.depth + 1, tree_width=args.width, budget=args.budget,
+                              algo=args.algo, target_layer_ids=head.target_layer_ids, sampling_params=sp,
+                              return_text=False, on_round=col)
+        if args.mode == "llm-depth-rank":
+            text = json.dumps(col.profile({"samples": len(prompts), "algo": args.algo, "width": args.width,
+                                           "budget": args.budget, "block_size": args.depth + 1}), indent=1)
+            if args.out:
+                open(args.out, "w").write(text)
+            print(text)
+        else:
+            print(json.dumps(conditioned_probe_verdict(col.marginal_ranks, col.conditioned_ranks, top=args.width)))
     else:
         ar_t = GpuTimer.patch(eng, "_forward")
         ar = eng.generate(prompts[0], sp)

@@ -141,7 +141,7 @@ class LLM:
                       sampling_params: SamplingParams = None, return_stats: bool = False,
                       profile_phases: bool = False, prompt_info: Optional[dict] = None,
                       profile_table: Optional[dict] = None, tree_attn: str = "sdpa",
-                      return_text: bool = True) -> dict:
+                      return_text: bool = True, on_round=None) -> dict:
         """Tree-speculative decode over a persistent cache.
 
         Per round: draft per-depth logits → build a tree of at most ``budget`` nodes →
@@ -149,6 +149,10 @@ class LLM:
         position ``past + depth[i]`` → accept the longest target-agreeing path plus a
         correction → compact the accepted nodes' KV behind the prefix.
         ``tree_attn`` is accepted for signature compatibility (one attention path here).
+        ``on_round`` (not in the reference's signature) is called after every round with a dict of that round's
+        ``committed`` ids and ``target_hidden`` as the drafter saw them, ``draft_logits``, ``tree``, the target's
+        ``target_argmax`` per node, the accepted ``path``, ``accepted`` length and ``correction`` token: the hook the
+        profiling collectors use instead of re-implementing the loop.
         Returns ``{"token_ids","tpf","decode_time",["text"],["accept_lengths","tree_sizes",
         "rounds",["phase_times"]]}``.
         """
@@ -191,6 +195,10 @@ class LLM:
                     path_l, acc, corr = tree_accept(tree, logits, sp.temperature)
             with timer.phase("kv_select"):
                 cache.select(past, path_l)
+            if on_round is not None:
+                on_round({"committed": committed, "target_hidden": target_hidden, "draft_logits": draft_logits,
+                          "tree": tree, "target_argmax": logits[0].argmax(-1), "path": list(path_l),
+                          "accepted": int(acc), "correction": int(corr)})
             if hid is not None:
                 target_hidden = torch.cat((target_hidden, hid[:, path_l]), 1)
             block = tree.token_ids[path_l[1:]].tolist() + [corr]

@@ -72,6 +72,89 @@ def shard_mlp(mlp, rank: int, world: int, interleave) -> dict:
     return {"gu": interleave(g, u), "gate": g, "up": u, "down": shard_cols(mlp.down_proj.weight, rank, world)}
 
 
+# --------------------------------------------------------------------------- buffer-ring rule (device-free)
+def ring_mod_for(calls_per_replay: int) -> int:
+    """Cycle length of the receive-buffer ring for a CUDA graph that issues ``calls_per_replay`` collectives.
+
+    Call ``c`` of a replay uses buffer ``c % ring_mod`` (baked into the graph).  Two collectives that follow
+    each other must not share a buffer (a fast rank's next push would meet cells its slow peer is still
+    reading), and that includes the last call of one replay and the first of the next:
+    ``calls_per_replay % ring_mod`` must not be 1.  A distance of two is preferred where a cycle length offers it.
+    For the few counts no cycle length of 2..6 satisfies (1, 61, 121, ...) the answer is 4 and the wrap-around is
+    covered by what every round of this engine ends with: the vocabulary-parallel argmax exchange, in which every
+    rank waits for every other rank, i.e. a full barrier between replays."""
+    for bad in ((1, 2), (1,)):
+        for r in (4, 5, 3, 6, 2):
+            if calls_per_replay % r not in bad:
+                return r
+    return 4
+
+
+class AllReduceRingModel:
+    """Executable model of the cell protocol of the fused all-reduce (two-shot by default, ``two_shot=False`` for
+    the one-shot form, whose finishing step consumes every rank's whole partial and has no gather step), for
+    checking the buffer-reuse rule without a GPU.
+
+    ``world`` ranks each run the same sequence of collectives; collective ``c`` uses ring buffer ``bufs[c]``.
+    A rank's steps per collective mirror the kernels: *push* (the GEMM epilogue stores this rank's slice cells
+    into every owner's first-phase buffer), *reduce* (the finishing kernel waits for all sources' cells of its
+    own slice, consumes and zeroes them, and stores the result cell into every rank's gather buffer), *gather*
+    (it waits for every owner's result cell, consumes and zeroes it).  ``run(schedule)`` interleaves the ranks
+    in any order the schedule function picks and raises ``AssertionError`` as soon as a store lands on a cell
+    whose previous content has not been consumed, or a rank consumes a value of another collective."""
+
+    def __init__(self, world: int, bufs: list, two_shot: bool = True):
+        self.world, self.bufs, self.two_shot = int(world), list(bufs), bool(two_shot)
+        n_buf = max(self.bufs) + 1
+        # rs[rank][buf][src] and ag[rank][buf][owner]: 0 = empty, else 1 + index of the collective that wrote it
+        self.rs = [[[0] * world for _ in range(n_buf)] for _ in range(world)]
+        self.ag = [[[0] * world for _ in range(n_buf)] for _ in range(world)]
+        self.pc = [0] * world          # 3 * collective + step
+
+    def _ready(self, r: int) -> bool:
+        c, step = divmod(self.pc[r], 3)
+        if c >= len(self.bufs):
+            return False
+        b = self.bufs[c]
+        if step == 0:
+            return True
+        cells = self.rs[r][b] if step == 1 else self.ag[r][b]
+        return all(v != 0 for v in cells)
+
+    def _step(self, r: int) -> None:
+        c, step = divmod(self.pc[r], 3)
+        b, tag = self.bufs[c], c + 1
+        if step == 0:
+            for o in range(self.world):
+                assert self.rs[o][b][r] == 0, f"collective {c}: rank {r} overwrote an unread first-phase cell of rank {o}"
+                self.rs[o][b][r] = tag
+        elif step == 1:
+            assert all(v == tag for v in self.rs[r][b]), f"collective {c}: rank {r} reduced cells of another collective"
+            self.rs[r][b] = [0] * self.world
+            for q in range(self.world):
+                if not self.two_shot:            # one shot: nothing to send, the "gather" step finds its cells set
+                    self.ag[r][b] = [tag] * self.world
+                    break
+                assert self.ag[q][b][r] == 0, f"collective {c}: rank {r} overwrote an unread gather cell of rank {q}"
+                self.ag[q][b][r] = tag
+        else:
+            assert all(v == tag for v in self.ag[r][b]), f"collective {c}: rank {r} gathered cells of another collective"
+            self.ag[r][b] = [0] * self.world
+        self.pc[r] += 1
+
+    def run(self, pick) -> int:
+        """Run to completion; ``pick(list of runnable ranks) -> rank``.  Returns the number of steps taken."""
+        steps = 0
+        while True:
+            ready = [r for r in range(self.world) if self._ready(r)]
+            if not ready:
+                break
+            self._step(pick(ready))
+            steps += 1
+        assert all(p == 3 * len(self.bufs) for p in self.pc), "the model deadlocked"
+        return steps
+
+
 # --------------------------------------------------------------------------- runtime
 class TensorParallel:
     """Process-group handle plus the peer buffers of the fused collectives."""
@@ -264,7 +347,7 @@ class TensorParallel:
         self._am_turn = 0
         self._tk_turn = 0
         if calls_per_replay is not None:
-            self.ring_mod = next(r for r in (4, 5, 3, 6) if calls_per_replay % r not in (1, 2))
+            self.ring_mod = ring_mod_for(calls_per_replay)
 
     def gemm_allreduce_nccl(self, x, w, out, residual=None):
         """Unfused baseline twin: library GEMM, NCCL all-reduce, residual add."""

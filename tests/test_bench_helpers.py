@@ -59,3 +59,28 @@ def test_reference_metric_rows():
     row = R.summarize("accum_logp", outs, [1.0], ar_tps=5.0, chain_tps=8.0)
     assert row["accept_len"] == pytest.approx(8 / 3) and row["e2e_tps"] == 10.0 and row["decode_tps"] == 20.0
     assert row["speedup_vs_ar"] == 2.0 and row["d0"] == pytest.approx(2 / 3) and row["d3"] == pytest.approx(1 / 3)
+
+
+def test_all_node_rank_counts_counts_every_parent():
+    all_node_rank_counts = P.all_node_rank_counts
+    # depth-0 root and two depth-1 nodes are parents; the depth-2 leaf is beyond the drafted depths (D = 2)
+    depths = [0, 1, 1, 2]
+    topk = [[10, 11], [20, 21]]
+    pick = [11, 20, 99, 5]                       # root -> rank 1; first child -> rank 0; second child -> not in top-k
+    hits, totals = all_node_rank_counts(depths, pick, topk)
+    assert totals == [1, 2] and hits == [[0, 1], [1, 0]]
+
+
+def test_llm_round_collector_runs_on_the_reference_engine_path():
+    """The LLM-path collector and the conditioned-vs-marginal probe run end to end on a tiny model."""
+    import subprocess, sys, os, json
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for mode in ("llm-depth-rank", "conditioned-probe"):
+        r = subprocess.run([sys.executable, os.path.join(root, "bench", "profiling.py"), mode, "--samples", "1",
+                            "--max-new", "12"], capture_output=True, text=True, cwd=root)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out = json.loads(r.stdout[r.stdout.index("{"):])
+        if mode == "llm-depth-rank":
+            assert len(out["depth_rank_accept"]) == 4 and sum(out["meta"]["trials"]) > 0
+        else:
+            assert out["verdict"] in ("P3_BUILD", "P3_SKIP") and "lift" in out

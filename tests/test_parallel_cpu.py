@@ -153,3 +153,37 @@ def test_data_parallel_reductions_over_gloo(tmp_path):
     mp.spawn(_dp_stats_worker, args=(2, _free_port(), out_path), nprocs=2, join=True)
     st = torch.load(out_path)
     assert st["tokens"] == 70 and st["wall_s"] == 2.0 and abs(st["tps"] - 35.0) < 1e-9 and abs(st["accept_len"] - 3.0) < 1e-9
+
+
+def test_allreduce_ring_rule_holds_under_any_interleaving():
+    """The receive-buffer ring of the fused all-reduce, as an executable model: for every number of collectives
+    per graph replay, the cycle length the runtime picks never lets a store land on an unread cell, whatever the
+    relative speed of the ranks; a ring of one buffer does, and the model says so."""
+    import random
+    from jetspec_b200.parallel.tp import AllReduceRingModel, ring_mod_for
+    rng = random.Random(0)
+    for world in (2, 4, 8):
+        for calls in list(range(2, 14)) + [36, 60, 62, 72, 73, 74, 96]:
+            mod = ring_mod_for(calls)
+            assert calls % mod != 1
+            bufs = [c % mod for c in range(calls)] * 4          # four replays of the same graph, back to back
+            for trial in range(6):
+                m = AllReduceRingModel(world, bufs, two_shot=trial % 2 == 0)
+                if trial == 0:
+                    m.run(lambda ready: ready[0])                # rank 0 always first
+                elif trial == 1:
+                    m.run(lambda ready: ready[-1])               # the last rank always first
+                else:
+                    m.run(lambda ready: rng.choice(ready))
+    assert ring_mod_for(1) == 4 and ring_mod_for(61) == 4      # no cycle length helps: covered by the round's barrier
+    # eager calls take buffers by call count modulo the same cycle: any cycle of two or more is safe ...
+    for two_shot in (True, False):
+        AllReduceRingModel(4, [c % 2 for c in range(9)], two_shot).run(lambda ready: rng.choice(ready))
+    # ... the two-shot form would even survive a single buffer (nobody can start the next collective before every
+    # rank has consumed its first-phase cells), the one-shot form does not: a fast rank's next push meets cells
+    # its slow peer has not consumed
+    AllReduceRingModel(4, [0] * 6).run(lambda ready: rng.choice(ready))
+    import pytest
+    with pytest.raises(AssertionError, match="overwrote"):
+        for _ in range(50):
+            AllReduceRingModel(4, [0] * 6, two_shot=False).run(lambda ready: rng.choice(ready))
