@@ -65,6 +65,10 @@ struct GemmParams {
   const float* row_weight;
   __nv_bfloat16* const* peer_pairs;
   int* const* peer_cnt;
+  // EPI_EP_COMBINE with token-sharded dispatch: row r of this rank's receive slab came from rank row_meta[r].x
+  // as that rank's (token, choice) pair row_meta[r].y; the weighted output row returns to that rank only, as
+  // flagged 8-byte cells {two bf16 values, 1} that the owner's finishing kernel polls (no counters)
+  const int2* row_meta;
   // NVFP4 mode: block scales of A and W in 512-byte tiles, per-row scale of A, per-tensor scale of W
   const uint8_t* sfa;
   const uint8_t* sfw;
@@ -392,12 +396,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int gr = m0 + prow, pc = gc + part * 8;
           if (gr >= m_end || pc >= p.N) continue;
           const uint4 d = *reinterpret_cast<const uint4*>(stage + prow * 64 + ((part ^ ((prow >> 1) & 3)) << 4));
+          if (p.row_meta != nullptr) {
+            const int2 m = p.row_meta[gr];
+            if (m.x < 0 || m.x >= p.world) continue;
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_pairs[m.x]) +
+                                      ((static_cast<size_t>(m.y) * p.N + pc) >> 1);
+            asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(d.x), "r"(1u), "r"(d.y), "r"(1u) : "memory");
+            asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "r"(d.z), "r"(1u), "r"(d.w), "r"(1u) : "memory");
+            continue;
+          }
           const size_t off = static_cast<size_t>(p.row_pair[gr]) * p.N + pc;
           for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peer_pairs[r] + off) = d;
         }
       }
       epi_barrier();
-      if (threadIdx.x == 64) {      // one release at system scope after the CTA barrier publishes every thread's stores
+      if (threadIdx.x == 64 && p.row_meta == nullptr) {      // one release at system scope after the CTA barrier publishes every thread's stores
         __threadfence_system();
         for (int r = 0; r < p.world; ++r) red_release_sys_add(p.peer_cnt[r], 1);
       }
@@ -979,6 +992,30 @@ extern "C" int js_gemm_bf16_grouped(const void* A, const void* W, void* C, int t
     return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
   }
   return -17;
+}
+
+// Experts' down projection of a token-sharded expert-parallel layer: grouped GEMM over this rank's receive slab
+// whose epilogue returns every weighted output row to the rank that owns the token (see GemmParams::row_meta).
+// A (slab_rows, K) rows grouped by local expert (group_off, groups + 1 entries), W (groups * N, K).
+extern "C" int js_gemm_bf16_grouped_ep(const void* A, const void* W, int slab_rows, int N, int K, int lda, int ldw,
+                                       int groups, const int* group_off, int max_rows_per_group, const void* row_meta,
+                                       const float* row_weight, void* const* peer_pairs, int world, int* status,
+                                       int pdl, cudaStream_t stream) {
+  using namespace js;
+  if (slab_rows <= 0 || groups <= 0) return 0;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || (N % 128)) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
+  if (!row_meta || !row_weight || !peer_pairs || world < 1) return -22;
+  CUtensorMap ta, tw;
+  if (make_map(&ta, A, slab_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128)) return -16;
+  GemmParams p{};
+  p.M = slab_rows; p.N = N; p.K = K; p.ldc = N; p.status = status; p.world = world;
+  p.group_off = group_off; p.row_weight = row_weight;
+  p.peer_pairs = reinterpret_cast<__nv_bfloat16* const*>(peer_pairs);
+  p.row_meta = reinterpret_cast<const int2*>(row_meta);
+  const int m_tiles = (max_rows_per_group + BM - 1) / BM;
+  if (m_tiles < 1) return 0;
+  return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
 }
 
 // NVFP4 GEMM: C[M,N] = (Aq * sfa * row_scale) * (Wq * sfw * w_scale)^T.  Aq (M, K/2) and Wq (N, K/2) hold two

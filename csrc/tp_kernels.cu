@@ -220,6 +220,11 @@ struct FinishNormParams {
   int ldx, ldh;
   float eps;
   int M, N, m_cap, world, rank, two_shot;
+  // one shot: the `world` sources of the 8 values at (row, c) sit at rs_recv + row * row_stride + c / 2 +
+  // src * src_stride (cells).  Tensor parallelism: (world, m_cap, N) -> row_stride N/2, src_stride m_cap*N/2.
+  // Expert-parallel combine: the "sources" are a token's k expert outputs, (T, k, H) -> row_stride k*H/2,
+  // src_stride H/2, summed in choice order.
+  size_t row_stride, src_stride;
   int* status;
 };
 
@@ -320,7 +325,6 @@ tp_finish_norm_kernel(FinishNormParams p) {
   // ---- phase 2 (or the whole job, one shot): one row per CTA turn
   unsigned long long* ag_mine = p.two_shot ? p.ag_peers[p.rank] : nullptr;
   const int groups = N >> 3;
-  const size_t one_stride = (static_cast<size_t>(p.m_cap) * N) >> 1;
   for (int row = blockIdx.x; row < p.M; row += gridDim.x) {
     uint4 keep[kFinishMaxGroups];
     float ss = 0.f;
@@ -349,8 +353,8 @@ tp_finish_norm_kernel(FinishNormParams p) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        unsigned long long* cells = p.rs_recv + ((static_cast<size_t>(row) * N + c) >> 1);
-        if (gather_sources(cells, one_stride, p.world, acc)) {
+        unsigned long long* cells = p.rs_recv + static_cast<size_t>(row) * p.row_stride + (c >> 1);
+        if (gather_sources(cells, p.src_stride, p.world, acc)) {
           if (p.residual != nullptr)
             add_bf16x8_plain(*reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.ldx + c), acc);
           ov = pack_bf16x8(acc);
@@ -560,6 +564,8 @@ extern "C" int js_tp_finish_norm(void* rs_recv, void* const* ag_peers, const voi
   p.h_out = reinterpret_cast<__nv_bfloat16*>(h_out);
   p.ldx = ldx; p.ldh = ldh; p.eps = eps;
   p.M = M; p.N = N; p.m_cap = m_cap; p.world = world; p.rank = rank; p.two_shot = two_shot;
+  p.row_stride = static_cast<size_t>(N) >> 1;
+  p.src_stride = (static_cast<size_t>(m_cap) * N) >> 1;
   p.status = status;
   cudaLaunchConfig_t c = {};
   c.gridDim = dim3(M < 2 * 148 ? M : 2 * 148);      // all CTAs resident (two per SM): see the deadlock note
@@ -592,4 +598,37 @@ extern "C" int js_tp_topk_combine(const float* part_val, const int* part_idx, co
   return cudaLaunchKernelEx(&c, js::tp_topk_combine_kernel, part_val, part_idx, part_lse, n_tiles, M, K, vocab_offset,
                             reinterpret_cast<unsigned long long* const*>(peer_buf), rank, world, m_cap, out_tok,
                             out_lp, status) == cudaSuccess ? 0 : -4;
+}
+
+// Owner side of the expert-parallel combine: pairs is THIS rank's (T, k, H) buffer of flagged cells that the
+// experts' down-projection epilogues of all ranks fill; out[t] = residual[t] + sum over the k choices of token t
+// in choice order, and (norm_w given) h_out = RMSNorm(out) * norm_w in the same pass.
+extern "C" int js_ep_combine_finish_norm(void* pairs, const void* residual, void* x_out, int ldx, const void* norm_w,
+                                         void* h_out, int ldh, float eps, int T, int H, int k, int* status, int pdl,
+                                         cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H % 8) || (ldx % 8) || (norm_w != nullptr && (ldh % 8))) return -10;
+  if (H > js::kFinishMaxGroups * js::kFinishThreads * 8 || k < 1 || k > js::kFinishMaxWorld) return -11;
+  js::FinishNormParams p;
+  p.rs_recv = reinterpret_cast<unsigned long long*>(pairs);
+  p.ag_peers = nullptr;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.x_out = reinterpret_cast<__nv_bfloat16*>(x_out);
+  p.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w);
+  p.h_out = reinterpret_cast<__nv_bfloat16*>(h_out);
+  p.ldx = ldx; p.ldh = ldh; p.eps = eps;
+  p.M = T; p.N = H; p.m_cap = T; p.world = k; p.rank = 0; p.two_shot = 0;
+  p.row_stride = (static_cast<size_t>(k) * H) >> 1;
+  p.src_stride = static_cast<size_t>(H) >> 1;
+  p.status = status;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(T < 2 * 148 ? T : 2 * 148);
+  c.blockDim = dim3(js::kFinishThreads);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::tp_finish_norm_kernel, p) == cudaSuccess ? 0 : -4;
 }

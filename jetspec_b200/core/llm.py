@@ -148,7 +148,9 @@ class LLM:
         ONE target forward over all nodes under the ancestor mask, node ``i`` at rotary
         position ``past + depth[i]`` → accept the longest target-agreeing path plus a
         correction → compact the accepted nodes' KV behind the prefix.
-        ``tree_attn`` is accepted for signature compatibility (one attention path here).
+        ``tree_attn``: ``"sdpa"`` (default) runs attention as the fp32 PyTorch formula, the in-repo oracle;
+        ``"triton"`` / ``"kernel"`` run it on the tcgen05 tree-attention kernel when the device, dtype and geometry
+        allow (see :meth:`ModelRunner.forward`), the counterpart of the reference's kernel switch for this path.
         ``on_round`` (not in the reference's signature) is called after every round with a dict of that round's
         ``committed`` ids and ``target_hidden`` as the drafter saw them, ``draft_logits``, ``tree``, the target's
         ``target_argmax`` per node, the accepted ``path``, ``accepted`` length and ``correction`` token: the hook the
@@ -164,9 +166,12 @@ class LLM:
         D = block_size - 1
         taps = list(target_layer_ids) if target_layer_ids is not None else None
         timer = PhaseTimer(enabled=profile_phases)
+        if tree_attn not in ("sdpa", "triton", "kernel"):
+            raise ValueError(f"unknown tree_attn {tree_attn!r}; expected 'sdpa', 'triton' or 'kernel'")
+        use_kernel = tree_attn != "sdpa"
         cache = self.runner.new_cache(committed.shape[1] + sp.max_new_tokens + budget + 2)
         logits, cache, target_hidden = self.runner.forward(committed, cache, target_layer_ids=taps,
-                                                           last_position_logits_only=True)
+                                                           last_position_logits_only=True, attn_kernel=use_kernel)
         first = self._pick(logits, sp.temperature)
         new_ids = [first]
         committed = torch.cat((committed, torch.tensor([[first]], device=self.device)), 1)
@@ -184,7 +189,8 @@ class LLM:
             with timer.phase("verify"):
                 pos = (past + tree.depth).reshape(1, -1)
                 logits, cache, hid = self.runner.forward(tree.token_ids.reshape(1, -1), cache, position_ids=pos,
-                                                         target_layer_ids=taps, ancestor=build_ancestor_matrix(tree))
+                                                         target_layer_ids=taps, ancestor=build_ancestor_matrix(tree),
+                                                         attn_kernel=use_kernel)
             rounds += 1
             with timer.phase("accept"):
                 if sp.temperature <= 0.0:

@@ -71,6 +71,28 @@ class ModelRunner:
         self.model = model
         self.cfg = model.config
 
+    def _kernel_attention_ok(self, ids: torch.Tensor, T: int, ancestor) -> bool:
+        cfg = self.cfg
+        w = self.model.lm_head.weight
+        if not (ids.is_cuda and w.dtype == torch.bfloat16 and cfg.head_dim == 128):
+            return False
+        if cfg.sliding_window and any(t == "sliding_attention" for t in (cfg.layer_types or [])):
+            return False
+        return ancestor is None or T <= 256
+
+    @staticmethod
+    def _kernel_attention_args(cache, past: int, T: int, ancestor, device) -> dict:
+        """The contiguous cache seen as a one-sequence paged pool: slot ``i`` is position ``i``."""
+        i32 = dict(dtype=torch.int32, device=device)
+        cap = cache.k[0].shape[1]
+        out = {"slot_map": torch.arange(cap, **i32).view(1, cap), "seq_rows": torch.zeros(1, **i32),
+               "cu_q": torch.tensor([0, T], **i32), "past": torch.tensor([past], **i32),
+               "mask_bits": None, "causal": ancestor is None}
+        if ancestor is not None:
+            from ..tree.ancestor import pack_ancestor_bits
+            out["mask_bits"] = pack_ancestor_bits(ancestor.to(device))
+        return out
+
     def new_cache(self, capacity: int = 512) -> DenseKVCache:
         p = self.model.lm_head.weight
         return DenseKVCache(self.cfg, p.device, p.dtype, capacity)
@@ -79,13 +101,18 @@ class ModelRunner:
     def forward(self, input_ids: torch.Tensor, past_key_values: Optional[DenseKVCache] = None,
                 position_ids: Optional[torch.Tensor] = None, output_hidden_states: bool = False,
                 target_layer_ids: Optional[Sequence[int]] = None, ancestor: Optional[torch.Tensor] = None,
-                last_position_logits_only: bool = False):
+                last_position_logits_only: bool = False, attn_kernel: bool = False):
         """Forward ``input_ids (1, T)``; new K/V are appended at ``cache.length``.
 
         ``ancestor (T, T) bool`` switches the new-token block from causal to tree
         masking: key ``j`` of the block is visible to query ``i`` iff
         ``ancestor[i, j]``; the cached prefix is always visible (sliding-window
         layers additionally hide keys further than the window behind the query).
+        ``attn_kernel`` runs attention on the tcgen05 tree-attention kernel over the contiguous cache (the
+        counterpart of the reference's dense tree-attention kernel for this path,
+        ``jetspec/core/tree_attention_kernel.py:63-216``) instead of the fp32 PyTorch formula; it applies on a CUDA
+        device with bf16 weights, ``head_dim`` 128, no sliding-window layers and at most 256 tree nodes, and is
+        ignored otherwise.
         Returns ``(logits (1, T or 1, V), cache, target_hidden (1, T, taps*H) or None)``.
         """
         cfg = self.cfg
@@ -104,10 +131,18 @@ class ModelRunner:
                          else torch.tril(torch.ones(T, T, dtype=torch.bool, device=ids.device)))
         key_pos = torch.cat((torch.arange(past, device=ids.device), pos))
         windows = {}
+        use_kernel = bool(attn_kernel) and self._kernel_attention_ok(ids, T, ancestor)
+        if use_kernel:
+            kern = self._kernel_attention_args(cache, past, T, ancestor, ids.device)
 
         def attn(layer: int, q, k, v):
             cache.k[layer][:, past:past + T] = k.transpose(0, 1)
             cache.v[layer][:, past:past + T] = v.transpose(0, 1)
+            if use_kernel:
+                from ..ops import cuda_ext as X
+                return X.paged_tree_attention(q.view(T, Hq, D).contiguous(), cache.k[layer], cache.v[layer],
+                                              kern["slot_map"], kern["seq_rows"], kern["cu_q"], kern["past"],
+                                              kern["mask_bits"], scale, kern["causal"], T, max_keys=past + T)
             K = cache.k[layer][:, :past + T].float()
             V = cache.v[layer][:, :past + T].float()
             qf = q.float().view(T, Hkv, g, D)

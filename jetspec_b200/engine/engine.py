@@ -100,7 +100,8 @@ class JetSpecEngine:
                  block_size: int = 16, attn_implementation: str = "sdpa", attn_backend: str = "sm100",
                  fuse_gemms: bool = False, torch_compile: bool = False, fused_moe: bool = False, *,
                  tokenizer=None, num_pages: Optional[int] = None, max_seqs: int = 64,
-                 max_seq_len: int = 8192, use_kernels: Optional[bool] = None, tensor_parallel=None):
+                 max_seq_len: int = 8192, use_kernels: Optional[bool] = None, tensor_parallel=None,
+                 expert_parallel=None):
         if attn_backend not in _BACKEND_ALIASES:
             raise ValueError(f"unknown attn_backend {attn_backend!r}; expected one of {sorted(_BACKEND_ALIASES)}")
         if isinstance(model_name_or_path, Qwen3ForCausalLM):
@@ -121,6 +122,9 @@ class JetSpecEngine:
         self.runner = ModelRunner(self.model)
         self.cfg = self.model.config
         self.tp = tensor_parallel      # jetspec_b200.parallel.TensorParallel or None
+        # jetspec_b200.parallel.TokenShardedEP or None: every rank decodes its OWN request (one engine call per
+        # rank, made together), the MoE layers' experts are sharded over the ranks
+        self.ep = expert_parallel
         self._num_pages = num_pages
         self._max_seqs, self._max_seq_len = int(max_seqs), int(max_seq_len)
         self.pool: Optional[PagedKVPool] = None

@@ -51,9 +51,9 @@ def local_dims(cfg, world: int = 1):
         num_hidden_layers=cfg.num_hidden_layers)
 
 
-def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
+def kernel_layer_weights(layers, cfg=None, tp=None, ep=None) -> list:
     """Kernel-ready per-layer weights: fused QKV (and K|V alone), tile-interleaved gate/up; with
-    tensor parallelism, this rank's shards of them."""
+    tensor parallelism, this rank's shards of them; with expert parallelism, this rank's experts."""
     out = []
     if tp is not None:
         from ..parallel.tp import shard_attention, shard_mlp
@@ -83,7 +83,12 @@ def kernel_layer_weights(layers, cfg=None, tp=None) -> list:
             d["down"] = layer.mlp.down_proj.weight
         else:   # sparse MoE: router + permutation kernels and two grouped GEMMs, all static-shape (no host read)
             m = layer.mlp
-            d["moe"] = (m.gate.weight, m.w_gate_up, m.w_down, int(m.top_k), bool(m.norm_topk_prob))
+            if ep is not None:
+                gu_l, dn_l = ep.shard(m.w_gate_up, m.w_down)
+                d["moe"] = (m.gate.weight, gu_l, dn_l, int(m.top_k), bool(m.norm_topk_prob))
+                d["moe_ep"] = True
+            else:
+                d["moe"] = (m.gate.weight, m.w_gate_up, m.w_down, int(m.top_k), bool(m.norm_topk_prob))
         out.append(d)
     return _finish_layer_weights(out)
 
@@ -194,7 +199,7 @@ class WeightPrefetcher:
 
 def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows, cu_q, past_lens, positions, slots,
                    mask_bits, causal: bool, freq, taps=None, tap_ids=None, pdl=True, tp=None, prefetch=None,
-                   then_prefetch=None, final_norm=None) -> int:
+                   then_prefetch=None, final_norm=None, ep=None) -> int:
     """Launch the kernels of ``len(layers)`` decoder layers on ``st.x`` (in place).  Returns the launch count.
 
     ``final_norm = (weight, out)`` also applies the model's last RMSNorm to the stack's output.  Under tensor
@@ -240,6 +245,24 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             X.rmsnorm(st.x, L["ln2"], eps, out=st.h, pdl=pdl)
         else:   # row-parallel: GEMM fused with the all-reduce over NVLink peer memory, finished together with ln2
             tp.gemm_allreduce(st.attn, L["o"], st.x, residual=st.x, pdl=pdl, norm_w=L["ln2"], norm_out=st.h, eps=eps)
+        if "moe" in L and L.get("moe_ep"):
+            # expert-parallel layer: this rank's rows travel to the experts' owners and back inside the kernels;
+            # the finishing kernel of the combine also computes the next RMSNorm
+            gate_w, gu_l, dn_l, top_k, renorm = L["moe"]
+            nw, nout = None, None
+            if li != last and not layers[li + 1].get("fp4"):
+                nw, nout, h_ready = layers[li + 1]["ln1"], st.h, True
+            elif li == last and final_norm is not None:
+                nw, nout = final_norm
+                final_norm = None
+            ep.moe_layer(st.x, st.h, gate_w, gu_l, dn_l, renorm, out=st.x, norm_w=nw, norm_out=nout, eps=eps, pdl=pdl)
+            n += 5 + merge_launch + 6          # + router GEMM, route + counts, dispatch, two grouped GEMMs, finish
+            if taps is not None and li != last:
+                for j, t in enumerate(tap_ids):
+                    if t == li:
+                        X.gather_rows(st.x, None, taps, dst_col0=j * H, pdl=pdl)
+                        n += 1
+            continue
         if "moe" in L:
             gate_w, w_gu, w_dn, top_k, renorm = L["moe"]
             st.x.add_(X.moe_forward(st.h, gate_w, w_gu, w_dn, top_k, renorm))
@@ -303,9 +326,12 @@ class FastRound:
         m = engine.model
         self.embed_w, self.lm_head_w, self.final_norm = m.model.embed_tokens.weight, m.lm_head.weight, m.model.norm.weight
         self.tp = getattr(engine, "tp", None)
+        self.ep = getattr(engine, "ep", None)
+        if self.tp is not None and self.ep is not None:
+            raise NotImplementedError("tensor parallelism and expert parallelism are separate plans here")
         world = self.tp.world if self.tp is not None else 1
         self.lcfg = local_dims(self.cfg, world)
-        self.layers = kernel_layer_weights(m.model.layers, self.cfg, self.tp)
+        self.layers = kernel_layer_weights(m.model.layers, self.cfg, self.tp, self.ep)
         if self.tp is not None:
             from ..parallel.tp import shard_rows
             self.vocab_local = self.cfg.vocab_size // world
@@ -397,14 +423,15 @@ class FastRound:
         if head is not None:
             self._draft_buffers(r, head)
         # run every kernel once outside capture (module load, function attributes), then capture
-        if self.tp is not None:
-            self.tp.begin_sequence()
+        par = self.tp if self.tp is not None else self.ep      # whichever runs collectives inside the round
+        if par is not None:
+            par.begin_sequence()
         r["launches"] = self._launch_round(r, pdl=False, use_remote=False)   # no handshakes while warming up
         torch.cuda.synchronize()
         X.status_word(dev).zero_()
-        if self.tp is not None:
-            self.tp.begin_sequence(self.tp._turn)     # cycle length that is safe across replays
-            r["ring_mod"] = self.tp.ring_mod
+        if par is not None:
+            par.begin_sequence(par._turn)     # cycle length that is safe across replays
+            r["ring_mod"] = par.ring_mod
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._launch_round(r, pdl=_PDL)
@@ -492,6 +519,8 @@ class FastRound:
                                 None if causal else d["full_mask"], causal, d["freq"], pdl=pdl)
         X.rmsnorm(st.x, hm.norm.weight, eps, out=d["hn"], pdl=pdl)
         rows = d["hn"][:bs - 1] if head.draft_shift else d["hn"][1:bs]
+        if r.get("no_topk"):                   # the caller wants the hidden rows only (dense-logits contract)
+            return n + 1
         if self.tp is None:
             X.lm_head_topk_logprobs(rows, head._fwd.lm_head_w, max(1, r["K"]), ws=d["tk_ws"], pdl=pdl,
                                     out_tok=d["topk_tok"], out_lp=d["topk_lp"])
@@ -533,7 +562,8 @@ class FastRound:
         n += 2 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
                                 r["cu_q"], r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"],
                                 False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp,
-                                prefetch=pf, then_prefetch=self.lm_head_w, final_norm=(self.final_norm, r["xn"]))
+                                prefetch=pf, then_prefetch=self.lm_head_w, final_norm=(self.final_norm, r["xn"]),
+                                ep=self.ep)
         last = cfg.num_hidden_layers - 1
         if r["taps"] is not None:
             for j, t in enumerate(r["tap_ids"]):
@@ -722,25 +752,40 @@ class FastRound:
                       dst=remote.draft_rank, group=remote.group)
             dist.send(hid, dst=remote.draft_rank, group=remote.group)
             remote.target_push_raw_header(0, first, 0)
-        if self.tp is not None:
-            self.tp.begin_sequence()      # the graph's collectives restart their buffer cycle here
-            self.tp.ring_mod = r.get("ring_mod", self.tp.ring_mod)
+        par = self.tp if self.tp is not None else self.ep
+        if par is not None:
+            par.begin_sequence()          # the graph's collectives restart their buffer cycle here
+            par.ring_mod = r.get("ring_mod", par.ring_mod)
         return first
+
+    def _all_max(self, v: int) -> int:
+        """Maximum of a host integer over the expert-parallel group."""
+        import torch.distributed as dist
+        t = torch.tensor([int(v)], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.ep.group)
+        return int(t.item())
+
+    def _all_done(self, mine_done: bool) -> bool:
+        """True once every rank of the expert-parallel group has finished its own request."""
+        import torch.distributed as dist
+        t = torch.tensor([1 if mine_done else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.ep.group)
+        return bool(int(t.item()))
 
     def _kernel_prefill_ok(self) -> bool:
         """The prompt runs through the same kernels as the rounds (fused QKV, in-kernel KV scatter, SwiGLU epilogue)
         whenever the layers are ones :func:`decoder_layers` covers; ``JETSPEC_EAGER_PREFILL=1`` keeps the module path."""
-        return self.tp is not None or os.environ.get("JETSPEC_EAGER_PREFILL", "0") != "1"
+        return self.tp is not None or self.ep is not None or os.environ.get("JETSPEC_EAGER_PREFILL", "0") != "1"
 
-    def _draft_prompt_context(self, r, hidden: torch.Tensor) -> int:
-        """Fill the draft head's context K/V for the prompt from the tapped hidden rows, with the same kernels the
-        in-graph context update uses (fc GEMM, RMSNorm, fused K|V GEMM, per-head norm + RoPE + scatter), in row
-        chunks.  Returns the number of context rows."""
+    def _draft_prompt_context(self, r, hidden: torch.Tensor, start: int = 0) -> int:
+        """Fill the draft head's context K/V for rows ``start ..`` of the tapped hidden states (the prompt), with
+        the same kernels the in-graph context update uses (fc GEMM, RMSNorm, fused K|V GEMM, per-head norm + RoPE +
+        scatter), in row chunks.  Returns the number of context rows."""
         d, hm = r["draft"], r["head"].head
         hc = hm.config
         n, Hkv, eps = hidden.shape[0], hc.num_key_value_heads, hc.rms_norm_eps
         hid = hidden.to(torch.bfloat16)
-        for s0 in range(0, n, 512):
+        for s0 in range(start, n, 512):
             rows = hid[s0:s0 + 512].contiguous()
             m = rows.shape[0]
             ctx = X.rmsnorm(X.gemm(rows, hm.fc.weight), hm.hidden_norm.weight, eps)
@@ -758,6 +803,8 @@ class FastRound:
         pool.reserve(sid, total)
         row = pool.state(sid).row
         chunk = 512 if self.tp is None else min(512, self.tp.m_cap)
+        if self.ep is not None:
+            chunk = min(chunk, self.ep.max_tokens)
         tap_ids = list(taps) if taps else None
         hidden = torch.empty(T, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
         seq_rows = torch.tensor([row], dtype=torch.int32, device=dev)
@@ -776,11 +823,20 @@ class FastRound:
             xn = torch.empty_like(st.x)
             decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, seq_rows, cu_q, past,
                            pos, slots, None, True, self.freq, taps=tapbuf, tap_ids=tap_ids, pdl=False, tp=self.tp,
-                           final_norm=(self.final_norm, xn))
+                           final_norm=(self.final_norm, xn), ep=self.ep)
             if tap_ids:
                 for j, t in enumerate(tap_ids):
                     if t == last:
                         hidden[s0:s0 + n, j * H:(j + 1) * H] = xn
+        if self.ep is not None:
+            # every rank takes part in every expert-parallel layer call: ranks with shorter prompts sit the
+            # remaining chunks out (their experts still serve the others' rows)
+            mine = (T + chunk - 1) // chunk
+            for _ in range(self._all_max(mine) - mine):
+                for L in self.layers:
+                    if L.get("moe_ep"):
+                        gate_w, gu_l, dn_l, _, renorm = L["moe"]
+                        self.ep.idle_layer(gate_w, gu_l, dn_l, renorm)
         h_last = xn[-1:].contiguous()
         out_idx = torch.empty(1, dtype=torch.int32, device=dev)
         nt = X.n_tiles(self.lm_head_w.shape[0])
@@ -831,8 +887,21 @@ class FastRound:
         src = oracle if oracle is not None else host_drafter
         stream = torch.cuda.current_stream()
         events = []
-        while len(new_ids) < sp.max_new_tokens and not done:
-            if staged and oracle is not None and hasattr(oracle, "propose_topk_at"):
+        frozen = None                      # expert parallelism: device state a finished rank keeps replaying from
+        final_len = None
+        while True:
+            active = len(new_ids) < sp.max_new_tokens and not done
+            if not active:
+                if self.ep is None:
+                    break
+                # this rank's request is over but others' are not: keep taking part in every layer's exchange by
+                # replaying the round from a fixed state (its own results are discarded, nothing advances)
+                if frozen is None:
+                    frozen, final_len = r["state"].clone(), int(res[4]) if rounds else None
+                r["state"].copy_(frozen)
+            if not active:
+                pass
+            elif staged and oracle is not None and hasattr(oracle, "propose_topk_at"):
                 tok_l, lp_l = oracle.propose_topk_at(len(ctx_ids), D, K)      # the script needs the position only
                 stage_tok[:] = np.asarray(tok_l, dtype=np.int32)
                 stage_lp[:] = np.asarray(lp_l, dtype=np.float32)
@@ -858,24 +927,31 @@ class FastRound:
             else:
                 r["graph"].replay()
             stream.synchronize()
-            rounds += 1
-            acc, n_nodes = int(res[0]), int(res[3])
-            if int(res[6]) != 0:
-                X.check_status(self.device)
-            block = res[8:8 + acc + 1].tolist()
-            accept_lengths.append(acc + 1)
-            tree_sizes.append(n_nodes)
-            if depth_hist is not None:
-                for dpt in r["depth"][:n_nodes].tolist():
-                    depth_hist[dpt] += 1
-            for t in block:
-                new_ids.append(int(t))
-                ctx_ids.append(int(t))
-                if int(t) in eng.eos_token_ids:
-                    done = True
-                    break
+            if active:
+                rounds += 1
+                acc, n_nodes = int(res[0]), int(res[3])
+                if int(res[6]) != 0:
+                    X.check_status(self.device)
+                block = res[8:8 + acc + 1].tolist()
+                accept_lengths.append(acc + 1)
+                tree_sizes.append(n_nodes)
+                if depth_hist is not None:
+                    for dpt in r["depth"][:n_nodes].tolist():
+                        depth_hist[dpt] += 1
+                for t in block:
+                    new_ids.append(int(t))
+                    ctx_ids.append(int(t))
+                    if int(t) in eng.eos_token_ids:
+                        done = True
+                        break
+                if final_len is None and (len(new_ids) >= sp.max_new_tokens or done):
+                    final_len = int(res[4])
+            if self.ep is not None and self._all_done(len(new_ids) >= sp.max_new_tokens or done):
+                break
+        if self.ep is not None:
+            X.check_status(self.device)
         if rounds:
-            eng.pool.state(sid).length = int(res[4])
+            eng.pool.state(sid).length = final_len if final_len is not None else int(res[4])
         if remote is not None:
             remote.target_push_raw_header(0, 0, 1)      # tell the drafter GPU this request is over
             torch.cuda.synchronize()
@@ -913,10 +989,21 @@ class FastRound:
         out = [first]
         res = r["result_host"].numpy()
         stream = torch.cuda.current_stream()
-        while len(out) < sp.max_new_tokens and out[-1] not in eng.eos_token_ids:
+        frozen = None
+        while True:
+            active = len(out) < sp.max_new_tokens and out[-1] not in eng.eos_token_ids
+            if not active:
+                if self.ep is None:
+                    break
+                if frozen is None:               # keep serving the other ranks' rows from a state that never advances
+                    frozen = r["state"].clone()
+                r["state"].copy_(frozen)
             r["graph"].replay()
             stream.synchronize()
-            if int(res[6]) != 0:
-                X.check_status(self.device)
-            out.append(int(res[8]))
+            if active:
+                if int(res[6]) != 0:
+                    X.check_status(self.device)
+                out.append(int(res[8]))
+            if self.ep is not None and self._all_done(len(out) >= sp.max_new_tokens or out[-1] in eng.eos_token_ids):
+                break
         return {"token_ids": out, "text": decode_text(eng.tokenizer, out)}

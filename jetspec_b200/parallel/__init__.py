@@ -2,5 +2,6 @@
 peer memory, expert parallelism for MoE layers, and their unfused NCCL baselines."""
 from .tp import TensorParallel, shard_rows, shard_cols, shard_attention, shard_mlp
 from .symm import SymmetricBuffer
+from .ep import ExpertParallel, TokenShardedEP
 
-__all__ = ["TensorParallel", "SymmetricBuffer", "shard_rows", "shard_cols", "shard_attention", "shard_mlp"]
+__all__ = ["TensorParallel", "ExpertParallel", "TokenShardedEP", "SymmetricBuffer", "shard_rows", "shard_cols", "shard_attention", "shard_mlp"]

@@ -46,3 +46,16 @@ def build_packed_ancestor_matrix(tree: DraftTree) -> torch.Tensor:
     if tree.ancestor_packed is None:
         tree.ancestor_packed = build_ancestor_matrix(tree).to(torch.uint8).contiguous()
     return tree.ancestor_packed
+
+
+def pack_ancestor_bits(ancestor: torch.Tensor) -> torch.Tensor:
+    """Bool ``(N, N)`` matrix -> ``(N, ceil(N/32))`` int32 words, bit ``j % 32`` of word ``j // 32`` = ``anc[i, j]``:
+    the mask format of the tree-attention kernels.  Works on the matrix's own device (no host round trip)."""
+    n = ancestor.shape[0]
+    words = max(1, (n + 31) // 32)
+    pad = torch.zeros(n, words * 32, dtype=torch.int64, device=ancestor.device)
+    pad[:, :n] = ancestor.to(torch.int64)
+    weights = (torch.ones(32, dtype=torch.int64, device=ancestor.device) << torch.arange(32, device=ancestor.device))
+    packed = (pad.view(n, words, 32) * weights).sum(-1)                  # values in [0, 2^32)
+    packed = torch.where(packed >= (1 << 31), packed - (1 << 32), packed)   # reinterpret as signed 32-bit
+    return packed.to(torch.int32).contiguous()

@@ -165,6 +165,63 @@ def test_in_graph_draft_head_matches_eager_head(engine, small, prompt):
     assert torch.allclose(lp, dev_lp, atol=0.05)
 
 
+def test_standalone_graphed_draft_head_matches_the_eager_head_and_serves_a_batch(stable_engine):
+    """``GraphedDraftHead`` on its own: one graph replay per call, the same proposals as the eager head (bf16
+    tolerance), a persistent context across calls, and one clone per request inside ``generate_tree_batch``."""
+    from jetspec_b200 import SamplingParams, DraftHeadTreeDrafter, GraphedDraftHead
+    from jetspec_b200.core.model_runner import ModelRunner
+    from jetspec_b200.models import DraftHeadModel, draft_head_config
+    model = stable_engine.model
+    hcfg = draft_head_config(model.config, num_layers=1, block_size=7, num_taps=3)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+    eager, graphed = DraftHeadTreeDrafter(head, model, block_size=7), GraphedDraftHead(head, model, block_size=7)
+    ids = torch.randint(0, 4096, (1, 60), generator=torch.Generator().manual_seed(2)).cuda()
+    _, _, hidden = ModelRunner(model).forward(ids, target_layer_ids=head.target_layer_ids)
+    for n in (40, 43, 49, 60):                       # a prompt, then three short extensions of the same context
+        ctx = ids[:, :n + 1]
+        t_e, lp_e = eager.propose_topk(ctx, 6, 4, target_hidden=hidden[:, :n])
+        t_g, lp_g = graphed.propose_topk(ctx, 6, 4, target_hidden=hidden[:, :n])
+        # the wide-margin model's log-probs run into the hundreds: compare relatively
+        assert float((t_e == t_g).float().mean()) > 0.8 and torch.allclose(lp_e, lp_g, atol=0.05, rtol=2e-2)
+        lg = graphed.propose_logits(ctx, 6, target_hidden=hidden[:, :n])
+        assert lg.shape == (1, 6, 4096)
+        assert float((lg[0].float().argmax(-1) == t_g[:, 0]).float().mean()) > 0.8
+    assert graphed.replays == 8 and len(graphed._gs["graphs"]) == 2      # captured once per output form, then replayed
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 4096, (1, n), generator=g) for n in (12, 70, 33)]
+    sp = SamplingParams(0.0, 24)
+    want = [[(int(p[0, -1]) + 1 + i) % 4096 for i in range(24)] for p in prompts]
+    outs = stable_engine.generate_tree_batch(prompts, graphed, block_size=7, tree_width=3, budget=24,
+                                             sampling_params=sp, target_layer_ids=head.target_layer_ids)
+    assert [o["token_ids"] for o in outs] == want
+
+
+def test_llm_path_tree_attention_kernel_is_lossless(stable_engine, prompt):
+    """The reference-engine path (``LLM``) with ``tree_attn="kernel"``: prefill and every tree forward run their
+    attention on the tcgen05 kernel over the contiguous cache, and decoding stays token-identical to greedy."""
+    from jetspec_b200 import LLM, SamplingParams, RandomTreeDrafter
+    from jetspec_b200.ops import cuda_ext
+    llm = LLM(stable_engine.model, device="cuda", dtype=torch.bfloat16)
+    sp = SamplingParams(0.0, 24)
+    expect = [(int(prompt[0, -1]) + 1 + i) % 4096 for i in range(24)]
+    assert llm.generate(prompt, sp)["token_ids"] == expect
+    calls = {"n": 0}
+    real = cuda_ext.paged_tree_attention
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    cuda_ext.paged_tree_attention = counting
+    try:
+        out = llm.generate_tree(prompt, RandomTreeDrafter(4096, seed=3), block_size=7, tree_width=3, budget=40,
+                                sampling_params=sp, return_stats=True, tree_attn="kernel")
+    finally:
+        cuda_ext.paged_tree_attention = real
+    assert out["token_ids"] == expect
+    assert calls["n"] == 4 * (1 + out["rounds"])            # every layer of the prefill and of each tree forward
+    cuda_ext.check_status("cuda")
+
+
 def test_session_reuses_graph(engine, prompt):
     from jetspec_b200 import SamplingParams, RandomTreeDrafter
     from jetspec_b200.engine.fast_round import FastRound

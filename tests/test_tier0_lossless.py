@@ -52,3 +52,18 @@ def test_temperature_sampling_runs(llm, tiny_prompt):
     out = llm.generate_tree(tiny_prompt, RandomTreeDrafter(1024, seed=1), block_size=5, tree_width=2, budget=8,
                             sampling_params=SamplingParams(0.8, 16))
     assert len(out["token_ids"]) == 16
+
+
+def test_tree_attn_switch_is_validated_and_harmless_on_cpu(tiny_model, tiny_prompt):
+    """``tree_attn="kernel"`` asks for the GPU attention kernel; on a CPU the request is ignored (same tokens as the
+    default), and an unknown value is an error."""
+    import pytest
+    from jetspec_b200 import LLM, SamplingParams, RandomTreeDrafter
+    llm = LLM(tiny_model, device="cpu", dtype=torch.float32)
+    sp = SamplingParams(0.0, 12)
+    kw = dict(block_size=5, tree_width=2, budget=8, sampling_params=sp)
+    a = llm.generate_tree(tiny_prompt, RandomTreeDrafter(tiny_model.config.vocab_size, seed=1), **kw)
+    b = llm.generate_tree(tiny_prompt, RandomTreeDrafter(tiny_model.config.vocab_size, seed=1), tree_attn="kernel", **kw)
+    assert a["token_ids"] == b["token_ids"] == llm.generate(tiny_prompt, sp)["token_ids"]
+    with pytest.raises(ValueError, match="tree_attn"):
+        llm.generate_tree(tiny_prompt, RandomTreeDrafter(tiny_model.config.vocab_size, seed=1), tree_attn="flash", **kw)

@@ -34,6 +34,12 @@ def test_tp_engine_two_ranks():
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
 
 
+def test_expert_parallel_engine_two_ranks():
+    """Token-sharded expert parallelism inside the engine: each rank's own request, sharded experts."""
+    rc, out = _launch(2, "ep_engine")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
 def test_disaggregated_draft_head_two_ranks():
     rc, out = _launch(2, "disagg")
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]

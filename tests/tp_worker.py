@@ -54,6 +54,45 @@ def disagg_main(rank):
     sys.exit(0 if int(flag) == 1 else 1)
 
 
+def ep_engine_main(rank, world):
+    """Expert-parallel engine: every rank decodes its OWN request (different prompt, different drafter, hence a
+    different number of rounds) while the experts are sharded; each rank's tokens must equal what a one-GPU
+    engine produces for that request."""
+    from jetspec_b200 import JetSpecEngine, SamplingParams, RandomTreeDrafter, OracleTreeDrafter
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config
+    from jetspec_b200.parallel import TokenShardedEP
+    from jetspec_b200.ops import cuda_ext as X
+    cfg = Qwen3Config(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
+                      num_attention_heads=8, num_key_value_heads=2, head_dim=128, num_experts=8,
+                      num_experts_per_tok=2, moe_intermediate_size=256, norm_topk_prob=True, model_type="qwen3_moe")
+    model = Qwen3ForCausalLM.random_init(cfg, seed=2, dtype=torch.bfloat16, device="cuda", init="stable")
+    dev = f"cuda:{torch.cuda.current_device()}"
+    prompt = torch.randint(0, cfg.vocab_size, (1, 20 + 9 * rank), generator=torch.Generator().manual_seed(rank))
+    sp = SamplingParams(0.0, 24 + 4 * rank)                    # ranks finish at different times
+    solo = JetSpecEngine(model, device=dev, dtype=torch.bfloat16, max_seq_len=512)
+    want = solo.generate(prompt, sp)["token_ids"]
+    ep = TokenShardedEP(None, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, max_tokens=128)
+    eng = JetSpecEngine(model, device=dev, dtype=torch.bfloat16, max_seq_len=512, expert_parallel=ep)
+    ar = eng.generate(prompt, sp)["token_ids"]
+    rnd = eng.generate_tree(prompt, RandomTreeDrafter(cfg.vocab_size, seed=3 + rank), tree_depth=4, tree_width=2,
+                            budget=8, sampling_params=sp, return_stats=True)
+    oracle = OracleTreeDrafter(prompt[0].tolist() + want, cfg.vocab_size, tree_width=3, mean_accept=2.0 + rank,
+                               max_accept=5, seed=rank)
+    orc = eng.generate_tree(prompt, oracle, tree_depth=6, tree_width=3, budget=16, sampling_params=sp, return_stats=True)
+    X.check_status("cuda")
+    ok = ar == want and rnd["token_ids"] == want and orc["token_ids"] == want
+    print(f"[rank {rank}] ep engine: AR ok {ar == want}, random-tree ok {rnd['token_ids'] == want} "
+          f"({rnd['rounds']} rounds), oracle-tree ok {orc['token_ids'] == want} ({orc['rounds']} rounds, "
+          f"{orc['tpf']:.2f} tokens/round)", flush=True)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_WORKER_OK" if int(flag) == 1 else "TP_WORKER_FAILED", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 1 else 1)
+
+
 def main():
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -61,6 +100,8 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     if len(sys.argv) > 1 and sys.argv[1] == "disagg":
         return disagg_main(rank)
+    if len(sys.argv) > 1 and sys.argv[1] == "ep_engine":
+        return ep_engine_main(rank, world)
     from jetspec_b200.ops import cuda_ext as X
     from jetspec_b200.parallel import TensorParallel, shard_cols, shard_rows
     X.load()
@@ -140,6 +181,7 @@ def main():
               flush=True)
     ok &= lp_err < 2e-2 and short < 2e-2 and same_t
     ok &= ep_check(rank, world)
+    ok &= ep_dispatch_check(rank, world)
     ok &= nvfp4_check(tp, rank, world)
     X.check_status("cuda")
     if len(sys.argv) > 1 and sys.argv[1] == "engine":
@@ -183,6 +225,51 @@ def ep_check(rank, world) -> bool:
     if rank == 0:
         print(f"ep moe layer: rel err {err:.2e} (nccl twin {err_b:.2e}), replicas identical {same}", flush=True)
     return err < 2e-2 and err_b < 2e-2 and same
+
+
+def ep_dispatch_check(rank, world) -> bool:
+    """Token-sharded expert parallelism: every rank brings its OWN tokens (different counts per rank, one rank
+    idle in one of the rounds); results against the single-device reference on those tokens."""
+    from jetspec_b200.parallel.ep import TokenShardedEP
+    from jetspec_b200.ops import reference as ref
+    E, H, I, k = 16, 512, 128, 4
+    g = torch.Generator(device="cuda").manual_seed(21)            # same seed: every rank builds the full weights
+    bf = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device="cuda") * sc).to(torch.bfloat16)
+    gate, wgu, wd = bf(E, H, sc=0.5), bf(E, 2 * I, H, sc=0.06), bf(E, H, I, sc=0.06)
+    nw = (1.0 + 0.1 * torch.randn(H, generator=g, device="cuda")).to(torch.bfloat16)
+    ep = TokenShardedEP(None, E, k, H, max_tokens=128)
+    gu_l, dn_l = ep.shard(wgu, wd)
+    good = True
+    worst = 0.0
+    for rnd in range(5):                                          # several turns of the buffer rings
+        T = [96, 37, 128, 1, 64, 80, 5, 100][(rank + rnd) % 8]
+        idle = rnd == 2 and rank == world - 1                     # one rank sits a round out
+        gl = torch.Generator(device="cuda").manual_seed(100 * rnd + rank)
+        x = torch.randn(T, H, generator=gl, device="cuda").to(torch.bfloat16)
+        hn = torch.randn(T, H, generator=gl, device="cuda").to(torch.bfloat16)
+        if idle:
+            ep.idle_layer(gate, gu_l, dn_l, True)
+            torch.cuda.synchronize()
+            continue
+        out, h2 = torch.empty_like(x), torch.empty_like(x)
+        ep.moe_layer(x, hn, gate, gu_l, dn_l, True, out=out, norm_w=nw, norm_out=h2, eps=1e-6)
+        torch.cuda.synchronize()
+        logits = hn.float() @ gate.float().t()
+        exp = x.float() + ref.moe_forward(hn.float(), gate.float(), wgu.float(), wd.float(), k, True, router_logits=logits)
+        err = float((out.float() - exp).abs().max() / exp.abs().max())
+        o32 = out.float()
+        h_ref = o32 * torch.rsqrt(o32.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+        err_n = float((h2.float() - h_ref).abs().max() / h_ref.abs().max())
+        worst = max(worst, err, err_n)
+        good &= err < 2e-2 and err_n < 2e-2
+    from jetspec_b200.ops import cuda_ext as X
+    X.check_status("cuda")
+    flag = torch.tensor([worst], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"ep token-sharded dispatch: worst rel err over ranks and rounds {float(flag):.2e}", flush=True)
+    ep.close()
+    return good
 
 
 def nvfp4_check(tp, rank, world) -> bool:
