@@ -292,7 +292,56 @@ __global__ void draft_prep_kernel(int* state, const int* committed, int mask_tok
   }
 }
 
+// Fan-out caps of one round from that round's per-depth top-k log-probs, on the device, so that algorithms other
+// than full fan-out keep the whole round inside one graph.  `plan_i` = {mode}, `plan_f` = {a, b} (doubles),
+// `templates` = 3 x D ints; the plan is per-request data in device memory, not a launch argument, so one captured
+// graph serves every algorithm.
+//   mode 0  caps[d] = templates[d]
+//   mode 1  caps[d] = max(1, round_half_even(K * sigmoid(-a * ((lp[d][0] - lp[d][1]) - b))))
+//   mode 2  g = mean over d of (lp[d][0] - lp[d][1]);  templates row 0 if g > a, row 1 if g < b, else row 2
+// Arithmetic in double, summed in depth order: the same numbers the host evaluator produces.
+__global__ void caps_from_topk_kernel(const float* topk_lp, int D, int K, const int* plan_i, const double* plan_f,
+                                      const int* templates, int* caps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int mode = plan_i[0];
+  const double a = plan_f[0], b = plan_f[1];
+  if (mode == 1 && K >= 2) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const double gap = static_cast<double>(topk_lp[d * K]) - static_cast<double>(topk_lp[d * K + 1]);
+      const double z = -a * (gap - b);
+      const double s = z >= 0.0 ? 1.0 / (1.0 + exp(-z)) : exp(z) / (1.0 + exp(z));
+      const int c = static_cast<int>(rint(static_cast<double>(K) * s));       // round half to even
+      caps[d] = c < 1 ? 1 : c;
+    }
+    return;
+  }
+  int row = 0;
+  if (mode == 2 && K >= 2) {
+    double sum = 0.0;
+    for (int d = 0; d < D; ++d) sum += static_cast<double>(topk_lp[d * K]) - static_cast<double>(topk_lp[d * K + 1]);
+    const double g = sum / static_cast<double>(D);
+    row = g > a ? 0 : (g < b ? 1 : 2);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) caps[d] = templates[row * D + d];
+}
+
 }  // namespace js
+
+extern "C" int js_caps_from_topk(const float* topk_lp, int D, int K, const int* plan_i, const double* plan_f,
+                                 const int* templates, int* caps, int pdl, cudaStream_t stream) {
+  if (D <= 0) return 0;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(64);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::caps_from_topk_kernel, topk_lp, D, K, plan_i, plan_f, templates, caps) == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int js_tree_build(const int* topk_tok, const float* topk_lp, const int* caps, int D, int K, int budget,
                              int NB, int W, const int* committed, int* state, const int* slot_map,

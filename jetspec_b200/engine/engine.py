@@ -332,7 +332,8 @@ class JetSpecEngine:
         algo_obj = get_algorithm(algo, **(algo_kwargs or {}))
         sid = self._new_seq_id()
         try:
-            if self.use_kernels and sp.temperature <= 0.0 and not extend_kwargs:
+            graph_sampling = sp.temperature <= 0.0 or (self.tp is None and self.ep is None)
+            if self.use_kernels and graph_sampling and not extend_kwargs:
                 from .fast_round import FastRound
                 fast = FastRound.get(self)
                 if fast.supports_tree(tree_drafter, algo_obj, block_size, tree_width, budget):

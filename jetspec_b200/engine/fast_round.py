@@ -13,6 +13,7 @@ Per-sequence device state (int32 words, see ``csrc/tree_kernels.cu``):
 """
 from __future__ import annotations
 
+import ctypes
 import math
 import os
 from typing import Optional
@@ -375,11 +376,12 @@ class FastRound:
 
     # ------------------------------------------------------------------ buffers + capture
     def _round(self, NB: int, D: int, K: int, budget: int, head: Optional[DraftHeadTreeDrafter], staged: bool,
-               tap_ids, max_new: int, remote=None):
+               tap_ids, max_new: int, remote=None, temperature: float = 0.0):
         pool = self.eng.pool
         tap_ids = list(tap_ids) if (tap_ids and (head is not None or remote is not None)) else None
+        temperature = float(temperature) if temperature > 0.0 else 0.0
         key = (NB, D, K, budget, id(head) if head is not None else 0, staged, tuple(tap_ids or ()), id(pool),
-               id(remote) if remote is not None else 0)
+               id(remote) if remote is not None else 0, temperature)
         if key in self.graphs:
             return self.graphs[key]
         if pool.resident():
@@ -398,6 +400,10 @@ class FastRound:
         r["topk_tok"] = _i32(Dn * Kn, dev).view(Dn, Kn)
         r["topk_lp"] = torch.zeros(Dn, Kn, dtype=torch.float32, device=dev)
         r["caps"] = _i32(Dn, dev, fill=K)
+        # the algorithm's per-request caps plan (see CapScheduleAlgorithm.device_caps_plan): mode, two doubles and
+        # three cap lists, evaluated on the device each round when the top-k comes from an in-graph head
+        r["plan_i"], r["plan_t"] = _i32(1, dev), _i32(3 * Dn, dev, fill=K)
+        r["plan_f"] = torch.zeros(2, dtype=torch.float64, device=dev)
         r["path_idx"] = _i32(64, dev)
         r["result"] = _i32(64, dev)
         r["result_host"] = torch.zeros(64, dtype=torch.int32).pin_memory()
@@ -415,6 +421,15 @@ class FastRound:
         r["am_ws"] = {"val": torch.zeros(NB, nt, dtype=torch.float32, device=dev),
                       "idx": torch.zeros(NB, nt, dtype=torch.int32, device=dev)}
         r["am_val"] = torch.zeros(NB, dtype=torch.float32, device=dev)
+        r["temperature"] = temperature
+        if temperature > 0.0:
+            # sampling keeps the round in the graph: the LM head writes fp32 logits for the NB nodes, one kernel
+            # draws a token per node (inverse CDF, uniforms from the graph-registered generator), and acceptance
+            # walks the tree against the SAMPLED tokens (reference: the graphed verify with the accept swapped,
+            # jetspec/inference_engine/engine.py:1084-1109)
+            r["logits"] = torch.zeros(NB, self.lm_head_w.shape[0], dtype=torch.float32, device=dev)
+            r["uniform"] = torch.zeros(NB, dtype=torch.float32, device=dev)
+            r["sampled"] = torch.zeros(NB, dtype=torch.int64, device=dev)
         r["taps"] = torch.zeros(NB, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
         if remote is not None:
             # the layer-epilogue copies write the tapped rows straight into the drafter GPU's buffer
@@ -479,6 +494,19 @@ class FastRound:
         d["freq"] = X.inv_freq(hc.head_dim, hc.rope_theta, dev)
         r["draft"] = d
 
+    @staticmethod
+    def _stage_caps_plan(r, plan: dict, D: int, K: int) -> None:
+        """Upload one request's caps plan (mode, parameters, up to three cap lists) for the in-graph caps kernel."""
+        mode = {"static": 0, "sigmoid": 1, "gap_select": 2}[plan["mode"]]
+        rows = {0: [plan.get("caps")], 1: [], 2: [plan.get("above"), plan.get("below"), plan.get("between")]}[mode]
+        t = torch.full((3, max(1, D)), K, dtype=torch.int32)
+        for i, row in enumerate(rows):
+            t[i, :D] = torch.tensor([int(c) for c in row[:D]], dtype=torch.int32)
+        ab = {0: (0.0, 0.0), 1: (plan.get("beta", 0.0), plan.get("g_0", 0.0)), 2: (plan.get("hi", 0.0), plan.get("lo", 0.0))}[mode]
+        r["plan_i"].copy_(torch.tensor([mode], dtype=torch.int32))
+        r["plan_f"].copy_(torch.tensor(ab, dtype=torch.float64))
+        r["plan_t"].copy_(t.reshape(-1))
+
     def _draft_lm_head(self, head) -> torch.Tensor:
         """The vocabulary matrix the draft head scores against: the target's (its shard under tensor parallelism)."""
         w = head._fwd.lm_head_w
@@ -540,6 +568,10 @@ class FastRound:
             if not r["staged"]:
                 r["topk_tok"].copy_(r["draft"]["topk_tok"][:D])
                 r["topk_lp"].copy_(r["draft"]["topk_lp"][:D])
+                lib.js_caps_from_topk.restype = ctypes.c_int
+                X._check(lib.js_caps_from_topk(p(r["topk_lp"]), D, max(1, K), p(r["plan_i"]), p(r["plan_f"]),
+                                               p(r["plan_t"]), p(r["caps"]), int(pdl), s()), "js_caps_from_topk")
+                n += 1
         remote = r.get("remote") if use_remote else None
         if remote is not None and D > 0:
             remote.target_wait_topk(pdl)
@@ -570,7 +602,16 @@ class FastRound:
                 if t == last:
                     X.gather_rows(r["xn"], None, r["taps"], dst_col0=j * cfg.hidden_size, pdl=pdl)
                     n += 1
-        if self.tp is None:
+        if r.get("temperature", 0.0) > 0.0:
+            X.gemm(r["xn"], self.lm_head_w, out=r["logits"], epi=X.EPI_STORE_F32, bn=128, split=1, pdl=pdl)
+            r["uniform"].uniform_()
+            lib.js_sample_temperature.restype = ctypes.c_int
+            X._check(lib.js_sample_temperature(p(r["logits"]), 0, NB, r["logits"].shape[1], r["logits"].stride(0),
+                                               ctypes.c_float(r["temperature"]), p(r["uniform"]), p(r["sampled"]), s()),
+                     "js_sample_temperature")
+            r["greedy"].copy_(r["sampled"])
+            n += 1
+        elif self.tp is None:
             X.lm_head_argmax(r["xn"], self.lm_head_w, ws=r["am_ws"], pdl=pdl, out_idx=r["greedy"], out_val=r["am_val"])
         else:
             self.tp.lm_head_argmax(r["xn"], self.lm_head_w, self.tp.rank * self.vocab_local, r["am_ws"], r["greedy"],
@@ -714,7 +755,7 @@ class FastRound:
         r["greedy_host"].copy_(r["greedy"], non_blocking=True)
 
     # ------------------------------------------------------------------ sequence setup
-    def _begin(self, r, sid: int, ids: torch.Tensor, taps, total: int) -> int:
+    def _begin(self, r, sid: int, ids: torch.Tensor, taps, total: int, temperature: float = 0.0) -> int:
         """Prefill through the eager kernel path and initialise the round's device state."""
         eng, pool = self.eng, self.eng.pool
         T = ids.shape[1]
@@ -725,11 +766,11 @@ class FastRound:
         if self.timing:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
-        if self._kernel_prefill_ok():
+        if self._kernel_prefill_ok() and temperature <= 0.0:
             first, hidden = self._prefill_kernels(sid, ids, taps, total)
-        else:
+        else:     # the module path returns the last row's logits, which a sampled first token needs
             logits, hidden = eng._prefill(sid, ids[0], taps=taps, reserve=total - T)
-            first = int(logits[-1].float().argmax())
+            first = int(sample(logits[-1], temperature)) if temperature > 0.0 else int(logits[-1].float().argmax())
         r["seq_rows"].fill_(pool.state(sid).row)
         state = torch.zeros(8, dtype=torch.int32)
         state[ST_PAST], state[ST_GEN] = T, 1
@@ -864,10 +905,13 @@ class FastRound:
         else:
             head, oracle, host_drafter = self._split_drafter(tree_drafter)
         staged = oracle is not None or host_drafter is not None
-        logit_free_caps = type(algo_obj).__name__ == "AccumLogP" or getattr(algo_obj, "force_baseline", False)
-        if (host_drafter is not None and taps is not None) or (head is not None and not staged and not logit_free_caps):
-            # a host drafter that conditions on hidden states, or fan-out caps that need the head's
-            # log-probs on the host, take the eager path
+        plan = None
+        if head is not None and not staged:
+            plan_fn = getattr(algo_obj, "device_caps_plan", None)
+            plan = plan_fn(D, K, prompt_info=prompt_info, profile_table=profile_table) if plan_fn is not None else None
+        if (host_drafter is not None and taps is not None) or (head is not None and not staged and plan is None):
+            # a host drafter that conditions on hidden states, or an algorithm whose caps have no device form,
+            # take the eager path
             return eng._generate_tree_eager(sid, committed, tree_drafter, algo_obj, algo_obj.name, None, block_size,
                                             tree_width, budget, taps, sp, return_stats, prompt_info, profile_table,
                                             tree_diag, max_depth, None, total)
@@ -875,8 +919,12 @@ class FastRound:
             taps = list(head.target_layer_ids) if taps is None else taps
             if head.block_size != block_size:
                 raise ValueError(f"draft head block_size {head.block_size} != block_size {block_size}")
-        r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens, remote=remote)
-        first = self._begin(r, sid, committed, taps if (head is not None or remote is not None) else None, total)
+        r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens, remote=remote,
+                        temperature=sp.temperature)
+        if plan is not None:
+            self._stage_caps_plan(r, plan, D, K)
+        first = self._begin(r, sid, committed, taps if (head is not None or remote is not None) else None, total,
+                            temperature=sp.temperature)
         new_ids = [first]
         ctx_ids = committed[0].tolist() + [first]
         accept_lengths, tree_sizes, rounds = [], [], 0

@@ -60,6 +60,20 @@ class CapScheduleAlgorithm(TreeAlgorithm):
     def caps_from_topk(self, topk_logprobs_cpu, tree_width, **kwargs) -> list:
         raise NotImplementedError
 
+    def device_caps_plan(self, D: int, K: int, prompt_info=None, profile_table=None) -> Optional[dict]:
+        """How a round's caps follow from that round's per-depth top-k log-probs, in a form a device kernel can
+        evaluate without the host (so an engine can keep drafting, tree building and verification in one graph):
+
+        * ``{"mode": "static", "caps": [D ints]}`` - the caps do not depend on the log-probs;
+        * ``{"mode": "sigmoid", "beta": b, "g_0": g}`` - ``max(1, round(K * sigmoid(-b (gap_d - g))))`` per depth;
+        * ``{"mode": "gap_select", "hi": h, "lo": l, "above": [...], "below": [...], "between": [...]}`` - one of
+          three cap lists by the mean top-1/top-2 gap ``g`` over the depths: ``g > hi``, ``g < lo``, otherwise.
+
+        Everything that depends on ``prompt_info`` / ``profile_table`` is resolved here, once per request.
+        :func:`eval_caps_plan` is the host evaluator (and the specification of the device kernel).  ``None`` means
+        the algorithm has no such form and its caps are computed on the host every round."""
+        return None
+
     def build(self, root_token, draft_logits, block_size, tree_width, budget, device,
               refresh_drafter_fn=None, profile_table=None, prompt_info=None, **kwargs) -> DraftTree:
         _check_logits(draft_logits, block_size)
@@ -78,6 +92,26 @@ class AccumLogP(CapScheduleAlgorithm):
     def caps_from_topk(self, topk_logprobs_cpu, tree_width, **kwargs):
         K = len(topk_logprobs_cpu[0]) if topk_logprobs_cpu else max(tree_width, 1)
         return [K] * len(topk_logprobs_cpu)
+
+    def device_caps_plan(self, D, K, prompt_info=None, profile_table=None):
+        return {"mode": "static", "caps": [int(K)] * int(D)}
+
+
+def eval_caps_plan(plan: dict, topk_logprobs, K: int) -> list:
+    """Evaluate a :meth:`CapScheduleAlgorithm.device_caps_plan` on one round's ``(D, K)`` log-probs (host lists).
+    Equal to the algorithm's own ``caps_from_topk`` for the request the plan was made for."""
+    D = len(topk_logprobs)
+    if plan["mode"] == "static":
+        return [int(c) for c in plan["caps"][:D]]
+    if plan["mode"] == "sigmoid":
+        return [sigmoid_cap(r[0] - r[1], K, plan["beta"], plan["g_0"]) for r in topk_logprobs]
+    g = _mean_top2_gap(topk_logprobs)
+    pick = "above" if g > plan["hi"] else "below" if g < plan["lo"] else "between"
+    return [int(c) for c in plan[pick][:D]]
+
+
+def _flat_lps(D: int, K: int) -> list:
+    return [[0.0] * int(K) for _ in range(int(D))]
 
 
 def sigmoid_cap(gap: float, K: int, beta: float, g_0: float) -> int:
@@ -99,6 +133,11 @@ class Top2GapFanout(CapScheduleAlgorithm):
         if K < 2:
             return [1] * len(topk_logprobs_cpu)
         return [sigmoid_cap(r[0] - r[1], K, self.beta, self.g_0) for r in topk_logprobs_cpu]
+
+    def device_caps_plan(self, D, K, prompt_info=None, profile_table=None):
+        if K < 2:
+            return {"mode": "static", "caps": [1] * int(D)}
+        return {"mode": "sigmoid", "beta": self.beta, "g_0": self.g_0}
 
 
 @register_tree_algo("depth_rank_histogram")
@@ -127,6 +166,9 @@ class DepthRankHistogram(CapScheduleAlgorithm):
             keep = sum(1 for r in range(min(K, len(row))) if row[r] >= self.tau)
             caps.append(min(K, max(1, keep)))
         return caps
+
+    def device_caps_plan(self, D, K, prompt_info=None, profile_table=None):
+        return {"mode": "static", "caps": self.caps_from_topk(_flat_lps(D, K), K, profile_table=profile_table)}
 
 
 CLASS_TEMPLATES = {
@@ -165,6 +207,18 @@ class _RouterBase(CapScheduleAlgorithm):
         self.gap_high, self.gap_low = float(gap_high), float(gap_low)
         self.templates = {k: list(v) for k, v in (templates or CLASS_TEMPLATES).items()}
         self.force_baseline = bool(force_baseline)
+
+    def device_caps_plan(self, D, K, prompt_info=None, profile_table=None):
+        """A caller label (or the baseline switch) fixes the caps for the request; otherwise the class follows the
+        mean-gap fingerprint of each round: three cap lists, one per class, made with the class as the label."""
+        flat = _flat_lps(D, K)
+        labelled = prompt_info is not None and isinstance(prompt_info.get("task"), str)
+        if self.force_baseline or labelled or K < 2:
+            return {"mode": "static", "caps": self.caps_from_topk(flat, K, prompt_info=prompt_info,
+                                                                  profile_table=profile_table)}
+        by = lambda cls: self.caps_from_topk(flat, K, prompt_info={"task": cls}, profile_table=profile_table)
+        return {"mode": "gap_select", "hi": self.gap_high, "lo": self.gap_low, "above": by("decisive_task"),
+                "below": by("uncertain_task"), "between": by("balanced_task")}
 
 
 @register_tree_algo("task_router")
@@ -256,6 +310,18 @@ class ReasoningRouter(CapScheduleAlgorithm):
         if looks_like_reasoning(prompt_info, topk_logprobs_cpu, self.gap_threshold):
             return [1] * D
         return _stretch(self.open_ended_template, D, K)
+
+    def device_caps_plan(self, D, K, prompt_info=None, profile_table=None):
+        D, K = int(D), max(int(K), 1)
+        if self.force_baseline:
+            return {"mode": "static", "caps": [K] * D}
+        if looks_like_reasoning(prompt_info, [], self.gap_threshold):       # the label / the prompt text decides
+            return {"mode": "static", "caps": [1] * D}
+        open_caps = _stretch(self.open_ended_template, D, K)
+        if K < 2:
+            return {"mode": "static", "caps": open_caps}
+        return {"mode": "gap_select", "hi": self.gap_threshold, "lo": float("-inf"), "above": [1] * D,
+                "below": open_caps, "between": open_caps}
 
 
 # --------------------------------------------------------------------------

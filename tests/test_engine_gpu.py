@@ -222,6 +222,95 @@ def test_llm_path_tree_attention_kernel_is_lossless(stable_engine, prompt):
     cuda_ext.check_status("cuda")
 
 
+def test_device_caps_kernel_matches_the_host_evaluator():
+    import ctypes
+    import random
+    from jetspec_b200.engine.fast_round import FastRound
+    from jetspec_b200.ops import cuda_ext as X
+    from jetspec_b200.tree import get_algorithm
+    from jetspec_b200.tree.algorithms import eval_caps_plan
+    lib = X.load()
+    lib.js_caps_from_topk.restype = ctypes.c_int
+    rng = random.Random(1)
+    D, K = 9, 7
+    i32 = dict(dtype=torch.int32, device="cuda")
+    r = {"plan_i": torch.zeros(1, **i32), "plan_t": torch.zeros(3 * D, **i32),
+         "plan_f": torch.zeros(2, dtype=torch.float64, device="cuda")}
+    caps = torch.zeros(D, **i32)
+    for name, kw, info in [("accum_logp", {}, None), ("top2gap_fanout", {"beta": 1.3, "g_0": 0.8}, None),
+                           ("task_router", {}, None), ("task_router", {}, {"task": "code"}),
+                           ("class_histogram", {}, None), ("reasoning_router", {"gap_threshold": 0.7}, None),
+                           ("depth_rank_histogram", {}, None)]:
+        algo = get_algorithm(name, **kw)
+        plan = algo.device_caps_plan(D, K, prompt_info=info)
+        FastRound._stage_caps_plan(r, plan, D, K)
+        for scale in (0.1, 0.6, 2.0, 5.0):
+            lps = [sorted((-rng.random() * scale * 3 for _ in range(K)), reverse=True) for _ in range(D)]
+            lp32 = torch.tensor(lps, dtype=torch.float32)
+            host = eval_caps_plan(plan, lp32.tolist(), K)          # the float32 values the device sees
+            assert host == algo.caps_from_topk(lp32.tolist(), K, prompt_info=info)
+            rc = lib.js_caps_from_topk(X._p(lp32.cuda()), D, K, X._p(r["plan_i"]), X._p(r["plan_f"]), X._p(r["plan_t"]),
+                                       X._p(caps), 0, X._stream())
+            assert rc == 0 and caps.tolist() == host, (name, scale)
+
+
+@pytest.mark.parametrize("algo,kw", [("accum_logp", {}), ("top2gap_fanout", {"beta": 2.0, "g_0": 0.5}),
+                                     ("depth_rank_histogram", {}), ("task_router", {}), ("class_histogram", {}),
+                                     ("reasoning_router", {})])
+def test_every_algorithm_stays_on_the_graph_path_with_an_in_graph_head(stable_engine, prompt, algo, kw, monkeypatch):
+    """A real draft head inside the round graph with every registered algorithm: the fan-out caps are computed by
+    the device kernel, the eager path is never entered, and decoding stays token-identical to greedy."""
+    from jetspec_b200 import SamplingParams, DraftHeadTreeDrafter
+    from jetspec_b200.models import DraftHeadModel, draft_head_config
+    model = stable_engine.model
+    hcfg = draft_head_config(model.config, num_layers=1, block_size=7, num_taps=3)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+
+    def no_eager(*a, **k):
+        raise AssertionError("the eager path was taken")
+    monkeypatch.setattr(stable_engine, "_generate_tree_eager", no_eager)
+    sp = SamplingParams(0.0, 24)
+    expect = [(int(prompt[0, -1]) + 1 + i) % 4096 for i in range(24)]
+    out = stable_engine.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=7), tree_depth=6,
+                                      tree_width=4, budget=24, algo=algo, algo_kwargs=kw, sampling_params=sp,
+                                      return_stats=True)
+    assert out["token_ids"] == expect
+    if algo == "reasoning_router":
+        # the same head asked for a chain by label: every tree is a path (one node per depth)
+        chain = stable_engine.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=7), tree_depth=6,
+                                            tree_width=4, budget=24, algo=algo, sampling_params=sp,
+                                            prompt_info={"mode": "reasoning"}, return_stats=True)
+        assert chain["token_ids"] == expect and max(chain["tree_sizes"]) <= 7
+
+
+def test_sampling_stays_on_the_graph_path(stable_engine, prompt, monkeypatch):
+    """Temperature > 0 keeps the graph-captured round (LM head writes logits, a kernel samples one token per node,
+    acceptance walks the tree against the sampled tokens).  At a tiny temperature sampling IS the argmax, so the
+    output must equal greedy decoding; at 0.7 the call completes with valid tokens and the same graph is replayed."""
+    from jetspec_b200 import SamplingParams, RandomTreeDrafter, OracleTreeDrafter
+    from jetspec_b200.engine.fast_round import FastRound
+    from jetspec_b200.ops import cuda_ext
+
+    def no_eager(*a, **k):
+        raise AssertionError("the eager path was taken")
+    monkeypatch.setattr(stable_engine, "_generate_tree_eager", no_eager)
+    expect = [(int(prompt[0, -1]) + 1 + i) % 4096 for i in range(32)]
+    oracle = OracleTreeDrafter(prompt[0].tolist() + expect, 4096, tree_width=3, mean_accept=3.0, max_accept=6, seed=4)
+    cold = stable_engine.generate_tree(prompt, oracle, tree_depth=6, tree_width=3, budget=24,
+                                       sampling_params=SamplingParams(1e-4, 32), return_stats=True)
+    assert cold["token_ids"] == expect and cold["tpf"] > 1.5
+    n_graphs = len(FastRound.get(stable_engine).graphs)
+    torch.manual_seed(0)
+    warm = stable_engine.generate_tree(prompt, RandomTreeDrafter(4096, seed=2), tree_depth=4, tree_width=2, budget=8,
+                                       sampling_params=SamplingParams(0.7, 32), return_stats=True)
+    again = stable_engine.generate_tree(prompt, RandomTreeDrafter(4096, seed=2), tree_depth=4, tree_width=2, budget=8,
+                                        sampling_params=SamplingParams(0.7, 32), return_stats=True)
+    assert len(warm["token_ids"]) == 32 and all(0 <= t < 4096 for t in warm["token_ids"])
+    assert len(again["token_ids"]) == 32
+    assert len(FastRound.get(stable_engine).graphs) == n_graphs + 1       # one graph for (bucket, T = 0.7), replayed
+    cuda_ext.check_status("cuda")
+
+
 def test_session_reuses_graph(engine, prompt):
     from jetspec_b200 import SamplingParams, RandomTreeDrafter
     from jetspec_b200.engine.fast_round import FastRound

@@ -177,3 +177,32 @@ def test_host_only_tree_carries_the_same_lists():
     host = build_from_topk("accum_logp", 11, toks, lps, 8, "host", tree_width=3)
     assert host.token_ids is None and host.num_nodes == full.num_nodes
     assert host.host == full.host == (full.token_ids.tolist(), full.parent_indices.tolist(), full.depth.tolist())
+
+
+def test_device_caps_plans_reproduce_every_algorithm():
+    """The per-request plan a device kernel evaluates gives the algorithm's own caps for any round's log-probs,
+    for every registered algorithm, with and without labels, profile tables and the baseline switch."""
+    import random
+    from jetspec_b200.tree import get_algorithm, list_algorithms
+    from jetspec_b200.tree.algorithms import eval_caps_plan
+    rng = random.Random(0)
+    D, K = 6, 5
+    table = {"depth_rank_accept": [[rng.random() * 0.1 for _ in range(K)] for _ in range(D)],
+             "per_class_histograms": {"decisive_task": [2, 1], "uncertain_task": [[0.5, 0.2, 0.0, 0.1, 0.0]] * D}}
+    cases = [("accum_logp", {}, None, None), ("top2gap_fanout", {"beta": 1.7, "g_0": 0.6}, None, None),
+             ("depth_rank_histogram", {"tau": 0.03}, None, table), ("depth_rank_histogram", {}, None, None),
+             ("task_router", {}, None, None), ("task_router", {}, {"task": "chat"}, None),
+             ("task_router", {"force_baseline": True}, None, None),
+             ("class_histogram", {}, None, table), ("class_histogram", {}, {"task": "math"}, table),
+             ("reasoning_router", {}, None, None), ("reasoning_router", {}, {"text": "Let me think. 2+2"}, None),
+             ("reasoning_router", {"gap_threshold": 0.4}, {"task": "poetry"}, None)]
+    assert {c[0] for c in cases} == set(list_algorithms())
+    for name, kw, info, prof in cases:
+        algo = get_algorithm(name, **kw)
+        plan = algo.device_caps_plan(D, K, prompt_info=info, profile_table=prof)
+        assert plan is not None and plan["mode"] in ("static", "sigmoid", "gap_select")
+        for scale in (0.05, 0.5, 1.5, 4.0):          # from near-flat to very peaked candidates
+            for _ in range(20):
+                lps = [sorted((-rng.random() * scale * 3 for _ in range(K)), reverse=True) for _ in range(D)]
+                want = algo.caps_from_topk(lps, K, prompt_info=info, profile_table=prof)
+                assert eval_caps_plan(plan, lps, K) == want, (name, kw, info)
