@@ -911,7 +911,9 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   const int kb_total = (K + BK - 1) / BK;
   if (split < 1 || split > 8 || split > kb_total) return -12;
   if ((epi == EPI_ARGMAX || epi == EPI_TOPK) && split != 1) return -13;
-  if (epi == EPI_SWIGLU && split > bn / 64) return -14;
+  // SwiGLU: the (gate, up) chunk pairs are dealt to the CTAs of the K-split cluster; with more CTAs than pairs
+  // (128-column tiles have two) the extra CTAs only contribute their partial products and own no output columns
+  if (epi == EPI_SWIGLU && split > 4) return -14;
   if ((epi == EPI_STORE || epi == EPI_STORE_F32) && split > bn / 32) return -14;
   if ((epi == EPI_STORE || epi == EPI_SWIGLU) && (ldc % 8)) return -15;
   CUtensorMap ta, tw;

@@ -236,7 +236,9 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None)
     kb = (K + 63) // 64
     split = 1
     if epi in (EPI_STORE, EPI_STORE_F32, EPI_SWIGLU):
-        max_split = 4 if epi != EPI_SWIGLU else 2
+        # SwiGLU tiles hold two (gate, up) chunk pairs, so a split of 4 leaves two CTAs of each cluster without
+        # output columns; it still pays when the projection is narrow (tensor-parallel shards: 24 tiles -> 96 CTAs)
+        max_split = 4
         # Measured on chains of L2-cold GEMMs (M = 128): a K split helps while the whole grid is one
         # wave of one CTA per SM AND the clusters can be placed (a cluster lives inside one GPC, so only
         # ~32 clusters of 4, ~40 of 3 or ~72 of 2 fit at once; 48 clusters of 3 ran as two waves).

@@ -184,6 +184,29 @@ class ExpertParallel:
             b.close()
 
 
+def slab_layout(counts, n_local: int):
+    """Where the dispatch kernel puts rows (device-free statement of ``ep_dispatch_kernel``'s placement).
+
+    ``counts[src][e]`` = number of (token, choice) pairs of source rank ``src`` routed to expert ``e``.  On the
+    rank that owns expert ``e`` (``e // n_local``) the receive slab is ordered by expert, and inside an expert by
+    source rank.  Returns ``(base, group_off)``: ``base[src][e]`` is the first slab row (on the owner of ``e``) of
+    ``src``'s rows of expert ``e``; ``group_off[owner]`` the ``n_local + 1`` row offsets of that owner's experts,
+    i.e. the row ranges its grouped GEMMs run over."""
+    world, E = len(counts), len(counts[0])
+    base = [[0] * E for _ in range(world)]
+    group_off = [[0] * (n_local + 1) for _ in range(E // n_local)]
+    for owner in range(E // n_local):
+        run = 0
+        for le in range(n_local):
+            e = owner * n_local + le
+            group_off[owner][le] = run
+            for src in range(world):
+                base[src][e] = run
+                run += counts[src][e]
+        group_off[owner][n_local] = run
+    return base, group_off
+
+
 class TokenShardedEP:
     """Expert parallelism over token-sharded ranks: peer-store dispatch, grouped expert GEMMs, combine in the
     down-projection epilogue (see the module docstring).  One instance serves every MoE layer of a model: the

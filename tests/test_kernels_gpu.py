@@ -69,7 +69,7 @@ def test_gemm_fp32_out(ext):
     assert rel_err(out, x.float() @ w.float().t()) < 1e-4
 
 
-@pytest.mark.parametrize("split", [1, 2])
+@pytest.mark.parametrize("split", [1, 2, 4])
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_swiglu(ext, split, bn):
     M, H, I = 77, 512, 1024

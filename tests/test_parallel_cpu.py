@@ -187,3 +187,31 @@ def test_allreduce_ring_rule_holds_under_any_interleaving():
     with pytest.raises(AssertionError, match="overwrote"):
         for _ in range(50):
             AllReduceRingModel(4, [0] * 6, two_shot=False).run(lambda ready: rng.choice(ready))
+
+
+def test_ep_slab_layout_is_a_partition():
+    """The placement rule of the expert-parallel dispatch: for any count matrix the row ranges that the sources
+    write on an owner are disjoint, each expert's rows are contiguous (all sources, in rank order), and together
+    they cover exactly the rows the owner's grouped GEMMs run over."""
+    import random
+    from jetspec_b200.parallel.ep import slab_layout
+    rng = random.Random(3)
+    for world, n_local in ((2, 4), (4, 2), (8, 16)):
+        E = world * n_local
+        for _ in range(10):
+            counts = [[rng.choice([0, 0, 1, 3, 17, 64]) for _ in range(E)] for _ in range(world)]
+            base, group_off = slab_layout(counts, n_local)
+            for owner in range(world):
+                covered = []
+                for le in range(n_local):
+                    e = owner * n_local + le
+                    lo = group_off[owner][le]
+                    for src in range(world):
+                        assert base[src][e] == lo                      # sources follow each other inside the expert
+                        covered.append((lo, lo + counts[src][e]))
+                        lo += counts[src][e]
+                    assert lo == group_off[owner][le + 1]
+                covered = [c for c in covered if c[1] > c[0]]
+                assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))      # no gap, no overlap
+                total = sum(counts[s][owner * n_local + le] for s in range(world) for le in range(n_local))
+                assert group_off[owner][n_local] == total
