@@ -5,6 +5,8 @@
     python bench/kernel_cases.py lm_head     # vocabulary GEMM with the argmax epilogue
     python bench/kernel_cases.py nvfp4       # activation quantiser + block-scaled GEMM on the same four shapes
     python bench/kernel_cases.py round_small # RMSNorm, norm+RoPE+KV scatter, draft top-k, tree build, accept+commit, KV compaction
+    python bench/kernel_cases.py collectives # the fused all-reduce tail + RMSNorm and the expert-parallel dispatch, with a world of ONE
+                                             # rank (every "peer" buffer is this GPU's own): the kernels' own cost without NVLink
 
 Each case holds well under a few GB on the device and launches its kernel a handful of times, so a
 profiler capture of it ends by itself.
@@ -127,9 +129,44 @@ def case_round_small(reps: int = 2):
     torch.cuda.synchronize()
 
 
+def case_collectives(reps: int = 3):
+    """The communication kernels on one GPU: a process group of one rank, so every push lands in this GPU's own
+    buffers.  Row-parallel o_proj / down_proj with the reduce-scatter epilogue + the finishing kernel that reduces,
+    gathers and applies the next RMSNorm (128 rows), and one token-sharded expert-parallel layer of the
+    Qwen3-30B-A3B geometry on 128 tokens (count exchange, dispatch, grouped GEMMs, combine + norm)."""
+    import torch.distributed as dist
+    from jetspec_b200.parallel import TensorParallel, TokenShardedEP
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29761")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    tp = TensorParallel(None, m_cap=128, n_max=4096)
+    M, H, I = 128, 4096, 12288
+    a, m = bf(M, H), bf(M, I)
+    wo, wd, nw = bf(H, H, scale=0.02), bf(H, I, scale=0.02), bf(H)
+    x, h = bf(M, H), torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    for _ in range(reps):
+        tp.gemm_allreduce(a, wo, x, residual=x, norm_w=nw, norm_out=h)
+        tp.gemm_allreduce(m, wd, x, residual=x, norm_w=nw, norm_out=h)
+    torch.cuda.synchronize()
+    E, He, Ie, k, T = 128, 2048, 768, 8, 128
+    ep = TokenShardedEP(None, E, k, He, max_tokens=T)
+    gate, wgu, wdn = bf(E, He, scale=0.5), bf(E, 2 * Ie, He, scale=0.03), bf(E, He, Ie, scale=0.03)
+    gu_l, dn_l = ep.shard(wgu, wdn)
+    xe, hn, nwe = bf(T, He), bf(T, He), bf(He)
+    out, h2 = torch.empty_like(xe), torch.empty_like(xe)
+    for _ in range(reps):
+        ep.moe_layer(xe, hn, gate, gu_l, dn_l, True, out=out, norm_w=nwe, norm_out=h2)
+    torch.cuda.synchronize()
+    X.check_status("cuda")
+    ep.close()
+    tp.close()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     X.load()
     {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4,
-     "round_small": case_round_small}[sys.argv[1]]()
+     "round_small": case_round_small, "collectives": case_collectives}[sys.argv[1]]()
     X.check_status("cuda")
     print("ok")

@@ -24,6 +24,12 @@ enum : int {
   kTimeoutPeer = 4,     // waited for a flag another GPU should have written
   kBadSlot = 5,         // a slot / page index fell outside the pool
   kBadNode = 6,         // a tree index fell outside the node range
+  kTimeoutEpCounts = 7,   // expert-parallel dispatch: a rank's per-expert counts never arrived
+  kTimeoutEpArrive = 8,   // expert-parallel dispatch: a source rank's rows never arrived
+  kTimeoutCellsReduce = 9,    // all-reduce tail, reduce step (or the expert-parallel combine): partial cells missing
+  kTimeoutCellsGather = 10,   // all-reduce tail, gather step: a slice owner's result cells missing
+  kTimeoutTopk = 11,      // vocabulary-parallel top-k: a rank's record never arrived
+  kEpOverflow = 12,       // more rows for one expert (or one rank) than the receive slab / the grouped launch covers
 };
 
 constexpr uint32_t kSpinLimit = 1u << 20;  // polls; each try_wait already suspends for a while

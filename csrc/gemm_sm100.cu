@@ -157,7 +157,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + data_bytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* accum_bar = empty_bar + kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* tmem_free = accum_bar + 1;       // grouped mode: the epilogue has drained the accumulator of a row tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -171,10 +172,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bx = lin / static_cast<int>(gridDim.y);
   }
   const int n0 = bx * BN;
-  const int m0 = grouped ? p.group_off[expert] + by * BM : by * BM;
+  const int m_first = grouped ? p.group_off[expert] + by * BM : by * BM;
   const int m_end = grouped ? p.group_off[expert + 1] : p.M;
   const int wn0 = expert * p.N + n0;         // row of this tile in the (stacked) weight matrix
-  if (m0 >= m_end) return;                   // this expert has fewer row tiles (uniform for the CTA)
+  if (m_first >= m_end) return;              // this expert has fewer row tiles (uniform for the CTA)
+  // Grouped mode: the launch covers gridDim.y row tiles per expert; an expert with more rows than that is still
+  // finished, because this CTA goes on to row tiles by + gridDim.y, by + 2 gridDim.y, ... of its expert (same
+  // weight tile, the pipeline simply keeps running; the accumulator is handed back and forth between the MMA
+  // issuer and the epilogue through `tmem_free`).  Every other mode processes exactly one tile.
+  const int tile_step = grouped ? static_cast<int>(gridDim.y) * BM : BM;
+  const int n_tiles_cta = grouped ? (m_end - m_first + tile_step - 1) / tile_step : 1;
+  int m0 = m_first;
   const int kb_total = (p.K + kKPerBlock - 1) / kKPerBlock;
   const int kb_begin = (kb_total * z) / split;
   const int kb_end = (kb_total * (z + 1)) / split;
@@ -189,6 +197,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(accum_bar, 1);
+    mbar_init(tmem_free, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -231,27 +240,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tma_load_2d(smem + i * S::kStage, &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0);
         load_sfa(i, kb_begin + i);
       }
-      for (int i = pre; i < nkb; ++i) {
-        const int s = i % kStages;
-        const uint32_t ph = (i / kStages) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) break;
-        mbar_expect_tx(&full_bar[s], S::kStage);
-        tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * kXStep, wn0);
-        tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * kXStep, m0);
-        load_sfw(s, kb_begin + i);
-        load_sfa(s, kb_begin + i);
+      bool p_ok = true;
+      for (int tj = 0; tj < n_tiles_cta && p_ok; ++tj) {
+        const int m_tile = m_first + tj * tile_step;
+        for (int i = (tj == 0 ? pre : 0); i < nkb; ++i) {
+          const int g = tj * nkb + i;              // running k-block count of this CTA
+          const int s = g % kStages;
+          if (g >= kStages) {
+            const uint32_t ph = (g / kStages) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) { p_ok = false; break; }
+          }
+          mbar_expect_tx(&full_bar[s], S::kStage);
+          tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * kXStep, wn0);
+          tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * kXStep, m_tile);
+          load_sfw(s, kb_begin + i);
+          load_sfa(s, kb_begin + i);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = FP4 ? umma_idesc_nvfp4(BM, BN) : umma_idesc_bf16(BM, BN);
       bool ok = true;
+      for (int tj = 0; tj < n_tiles_cta && ok; ++tj) {
+      if (tj > 0) {                 // the epilogue must have read the previous row tile out of tensor memory
+        ok = mbar_wait(tmem_free, (tj - 1) & 1, p.status, kTimeoutAccum);
+        if (!ok) break;
+        tc_fence_after();
+      }
       for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % kStages;
-        const uint32_t ph = (i / kStages) & 1;
+        const int g = tj * nkb + i;
+        const int s = g % kStages;
+        const uint32_t ph = (g / kStages) & 1;
         ok = mbar_wait(&full_bar[s], ph, p.status, kTimeoutFull);
         if (!ok) break;
-        if (i == 0) JS_TRACE(2);   // first stage landed
+        if (g == 0) JS_TRACE(2);   // first stage landed
         tc_fence_after();
         const uint64_t a_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage));
         const uint64_t b_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage + S::kStageA));
@@ -281,6 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
       }
       umma_commit(accum_bar);         // accumulator complete (also releases the epilogue on error)
+      }
     }
   }
 
@@ -288,7 +312,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool epi_warp = warp >= 2;
   const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
   const int row = quad * 32 + lane;              // row of the tile owned by this thread
-  const int grow = m0 + row;
   const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
   // split-K: this CTA's receive area (after the pipeline stages) and the chunk -> owner mapping
   constexpr bool kSwiglu = (EPI == EPI_SWIGLU);
@@ -301,9 +324,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto local_of = [&](int ch) { return (ch % kHC) / split + (ch >= kHC ? per_owner : 0); };
   bool acc_ok = true;
 
+  for (int tj = 0; tj < n_tiles_cta; ++tj) {     // one pass, except for a grouped-mode expert with many rows
+  m0 = m_first + tj * tile_step;
+  const int grow = m0 + row;
   if (epi_warp) {
     pdl_wait();   // residual / C may be produced by the previous kernel
-    acc_ok = mbar_wait(accum_bar, 0, p.status, kTimeoutAccum);
+    acc_ok = mbar_wait(accum_bar, tj & 1, p.status, kTimeoutAccum);
     tc_fence_after();
     if (threadIdx.x == 64) JS_TRACE(3);   // accumulator complete
   }
@@ -801,6 +827,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         p.part_lse[o * 2 + 1] = se;
       }
     }
+  }
+  if (tj + 1 < n_tiles_cta && epi_warp) {        // hand the accumulator back for the CTA's next row tile
+    tc_fence_before();
+    epi_barrier();
+    if (threadIdx.x == 64) mbar_arrive(tmem_free);
+  }
   }
 
   // ------------------------------------------------------------------ teardown

@@ -299,7 +299,7 @@ tp_finish_norm_kernel(FinishNormParams p) {
   __shared__ float s_inv;
   const int tid = threadIdx.x;
   const int N = p.N;
-  bool ok = true;
+  bool ok = true, ok2 = true;
 
   if (p.two_shot) {
     // ---- phase 1: reduce this rank's column slice, broadcast the rounded result
@@ -347,7 +347,7 @@ tp_finish_norm_kernel(FinishNormParams p) {
           ov = make_uint4(a.x, a.z, b.x, b.z);
           zero_cells4(cells);
         } else {
-          ok = false;
+          ok2 = false;
         }
       } else {
         float acc[8];
@@ -399,7 +399,8 @@ tp_finish_norm_kernel(FinishNormParams p) {
       __syncthreads();                  // red / s_inv are reused by the next row
     }
   }
-  if (!ok) report(p.status, kTimeoutPeer);
+  if (!ok) report(p.status, kTimeoutCellsReduce);
+  if (!ok2) report(p.status, kTimeoutCellsGather);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -455,7 +456,7 @@ tp_topk_combine_kernel(const float* part_val, const int* part_idx, const float* 
   }
   __syncthreads();
   if (s_bad) {
-    if (tid == 0) report(status, kTimeoutPeer);
+    if (tid == 0) report(status, kTimeoutTopk);
     return;
   }
   if (tid == 0) {

@@ -270,8 +270,11 @@ tree_accept_commit_kernel(const int* tokens, const int* parents, const int* dept
 // positions / slots / block token ids of one draft-head step.  The block is
 // [anchor, mask, mask, ...]; its rows sit at positions ctx .. ctx+bs-1 where ctx is the
 // context length AFTER this round's new rows (state[ST_CTX] + state[ST_NEW]).
+// `fill` (optional): n_fill tokens, `fill_stride` ints apart, that replace the first mask tokens of the block - the
+// path-conditioned form of the step (the block then reads [anchor, fill_0, fill_1, ..., mask, ...]).
 __global__ void draft_prep_kernel(int* state, const int* committed, int mask_token, int bs, int rows_pad,
-                                  int ctx_rows_pad, int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out) {
+                                  int ctx_rows_pad, int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out,
+                                  const int* fill, int fill_stride, int n_fill) {
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x;
@@ -280,7 +283,8 @@ __global__ void draft_prep_kernel(int* state, const int* committed, int mask_tok
   const int ctx = ctx_old + n_new;
   const int past = state[ST_PAST];
   for (int i = tid; i < rows_pad; i += blockDim.x) {
-    block_ids[i] = (i == 0) ? committed[past] : mask_token;
+    block_ids[i] = (i == 0) ? committed[past]
+                            : ((fill != nullptr && i - 1 < n_fill) ? fill[(i - 1) * fill_stride] : mask_token);
     block_pos[i] = ctx + i;
   }
   for (int i = tid; i < ctx_rows_pad; i += blockDim.x) ctx_pos[i] = ctx_old + i;
@@ -290,6 +294,58 @@ __global__ void draft_prep_kernel(int* state, const int* committed, int mask_tok
     state[ST_CTX] = ctx;
     state[ST_NEW] = 0;
   }
+}
+
+// Gate of the tree extension ("ceiling raise"): fires when the drafter's rank-1 chain is fully present in the built
+// tree and the mean top-1 / top-2 gap along it exceeds the threshold, and there is room for `ext` more nodes.
+// out = {fire, leaf node of the chain, node count}.  One thread: the tree has at most a few hundred nodes.
+__global__ void tree_ext_gate_kernel(const int* tokens, const int* parents, const int* state, const int* topk_tok,
+                                     const float* topk_lp, int D, int K, float gap_threshold, int ext, int NB,
+                                     int* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0) return;
+  const int n = state[ST_NNODES];
+  int node = 0, fire = (K >= 2 && D > 0 && n + ext <= NB) ? 1 : 0;
+  float gap = 0.f;
+  for (int d = 0; d < D && fire; ++d) {
+    const int want = topk_tok[d * K];
+    int child = -1;
+    for (int i = node + 1; i < n; ++i)
+      if (parents[i] == node && tokens[i] == want) { child = i; break; }
+    if (child < 0) fire = 0;
+    node = child;
+    gap += topk_lp[d * K] - topk_lp[d * K + 1];
+  }
+  if (fire && !(gap / static_cast<float>(D) > gap_threshold)) fire = 0;
+  out[0] = fire;
+  out[1] = fire ? node : 0;
+  out[2] = n;
+}
+
+// Chain extension: `ext` nodes, one under the other, below `leaf`; their tokens are the argmax of the first `ext`
+// rows of the path-conditioned draft pass.  Rows n .. n+ext-1 of the round's tree arrays were pad rows (their KV
+// slots are already assigned); they become real nodes here and the node count grows.
+__global__ void tree_ext_splice_kernel(int* tokens, int* parents, int* depth, int* positions, int* mask_bits,
+                                       int* state, const int* gate, const int* ext_tok, int ext, int NB, int W,
+                                       int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0 || gate[0] == 0) return;
+  const int leaf = gate[1], n = gate[2], past = state[ST_PAST];
+  if (leaf < 0 || leaf >= n || n + ext > NB) {
+    report(status, kBadNode);
+    return;
+  }
+  for (int i = 0; i < ext; ++i) {
+    const int idx = n + i, par = (i == 0) ? leaf : idx - 1;
+    tokens[idx] = ext_tok[i];
+    parents[idx] = par;
+    depth[idx] = depth[par] + 1;
+    positions[idx] = past + depth[idx];
+    for (int w = 0; w < W; ++w) mask_bits[idx * W + w] = mask_bits[par * W + w] | ((w == (idx >> 5)) ? (1 << (idx & 31)) : 0);
+  }
+  state[ST_NNODES] = n + ext;
 }
 
 // Fan-out caps of one round from that round's per-depth top-k log-probs, on the device, so that algorithms other
@@ -327,6 +383,39 @@ __global__ void caps_from_topk_kernel(const float* topk_lp, int D, int K, const 
 }
 
 }  // namespace js
+
+extern "C" int js_tree_ext_gate(const int* tokens, const int* parents, const int* state, const int* topk_tok,
+                                const float* topk_lp, int D, int K, float gap_threshold, int ext, int NB, int* out,
+                                int pdl, cudaStream_t stream) {
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(32);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::tree_ext_gate_kernel, tokens, parents, state, topk_tok, topk_lp, D, K,
+                            gap_threshold, ext, NB, out) == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int js_tree_ext_splice(int* tokens, int* parents, int* depth, int* positions, int* mask_bits, int* state,
+                                  const int* gate, const int* ext_tok, int ext, int NB, int W, int* status, int pdl,
+                                  cudaStream_t stream) {
+  if (ext < 1 || NB > js::kMaxNodes || W < 1 || W > js::kMaxWords) return -10;
+  cudaLaunchConfig_t c = {};
+  c.gridDim = dim3(1);
+  c.blockDim = dim3(32);
+  c.stream = stream;
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  c.attrs = &a;
+  c.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&c, js::tree_ext_splice_kernel, tokens, parents, depth, positions, mask_bits, state, gate,
+                            ext_tok, ext, NB, W, status) == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int js_caps_from_topk(const float* topk_lp, int D, int K, const int* plan_i, const double* plan_f,
                                  const int* templates, int* caps, int pdl, cudaStream_t stream) {
@@ -380,9 +469,20 @@ extern "C" int js_tree_accept_commit(const int* tokens, const int* parents, cons
                             status) == cudaSuccess ? 0 : -4;
 }
 
+extern "C" int js_draft_prep_fill(int* state, const int* committed, int mask_token, int bs, int rows_pad,
+                                  int ctx_rows_pad, int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out,
+                                  const int* fill, int fill_stride, int n_fill, int pdl, cudaStream_t stream);
+
 extern "C" int js_draft_prep(int* state, const int* committed, int mask_token, int bs, int rows_pad, int ctx_rows_pad,
                              int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out, int pdl,
                              cudaStream_t stream) {
+  return js_draft_prep_fill(state, committed, mask_token, bs, rows_pad, ctx_rows_pad, block_ids, block_pos, ctx_pos,
+                            n_new_out, nullptr, 0, 0, pdl, stream);
+}
+
+extern "C" int js_draft_prep_fill(int* state, const int* committed, int mask_token, int bs, int rows_pad,
+                                  int ctx_rows_pad, int* block_ids, int* block_pos, int* ctx_pos, int* n_new_out,
+                                  const int* fill, int fill_stride, int n_fill, int pdl, cudaStream_t stream) {
   cudaLaunchConfig_t c = {};
   c.gridDim = dim3(1);
   c.blockDim = dim3(64);
@@ -393,5 +493,5 @@ extern "C" int js_draft_prep(int* state, const int* committed, int mask_token, i
   c.attrs = &a;
   c.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&c, js::draft_prep_kernel, state, committed, mask_token, bs, rows_pad, ctx_rows_pad,
-                            block_ids, block_pos, ctx_pos, n_new_out) == cudaSuccess ? 0 : -4;
+                            block_ids, block_pos, ctx_pos, n_new_out, fill, fill_stride, n_fill) == cudaSuccess ? 0 : -4;
 }

@@ -168,7 +168,13 @@ def status_word(device) -> torch.Tensor:
 
 STATUS_NAMES = {0: "ok", 1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free stage",
                 3: "timeout waiting for the accumulator", 4: "timeout waiting for a peer flag",
-                5: "KV slot out of range", 6: "tree node index out of range"}
+                5: "KV slot out of range", 6: "tree node index out of range",
+                7: "expert-parallel dispatch: a rank's expert counts never arrived",
+                8: "expert-parallel dispatch: a source rank's rows never arrived",
+                9: "all-reduce tail / expert combine: partial cells never arrived",
+                10: "all-reduce tail: a slice owner's result cells never arrived",
+                11: "vocabulary-parallel top-k: a rank's record never arrived",
+                12: "expert-parallel dispatch: more rows for one expert than the grouped launch covers"}
 
 
 def check_status(device) -> None:
@@ -195,6 +201,7 @@ def inv_freq(head_dim: int, theta: float, device) -> torch.Tensor:
 EPI_STORE, EPI_SWIGLU, EPI_ARGMAX, EPI_TOPK, EPI_STORE_F32 = 0, 1, 2, 3, 4
 SM_COUNT = 148
 _DEEP = os.environ.get("JETSPEC_GEMM_DEEP", "0") == "1"
+_SPLIT_DEEP = int(os.environ.get("JETSPEC_SPLIT_DEEP", "1"))
 
 
 # measured best (bn, split, deep) per (M, N, K, epilogue); filled from the tuning sweep
@@ -248,7 +255,10 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None)
                 split = c
                 break
     if split > 1:
-        return bn, split, 1            # deep pipeline; the receive area aliases the stages
+        # deep pipeline (192 KB, one CTA per SM; the receive area aliases the stages) unless JETSPEC_SPLIT_DEEP picks
+        # 2 (128 KB) or 0 (96 KB: two kernels' CTAs can share an SM, so the next kernel's prologue and first weight
+        # stages overlap this one's epilogue)
+        return bn, split, _SPLIT_DEEP
     # no split: a deep pipeline when the tiles fit one CTA per SM, else two shallow CTAs per SM
     return bn, 1, (1 if tiles <= SM_COUNT or _DEEP else 0)
 
@@ -633,11 +643,14 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
     h = torch.empty(T * top_k, I, dtype=x.dtype, device=x.device)
     ys = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
     st = _p(status_word(x.device))
+    # launch for a few times the balanced rows per expert (an expert can hold at most T rows); hotter experts are
+    # finished by their CTAs walking on through the remaining row tiles, empty tiles are never launched in bulk
+    cover = min(T, ((4 * T * top_k // E + 128 + 127) // 128) * 128)
     _check(lib.js_gemm_bf16_grouped(_p(xs), _p(gu), _p(h), T * top_k, 2 * I, H, xs.stride(0), gu.stride(0), h.stride(0),
-                                    EPI_SWIGLU, E, _p(group_off), T, None, None, None, None, 1, st, 0, _stream()),
+                                    EPI_SWIGLU, E, _p(group_off), cover, None, None, None, None, 1, st, 0, _stream()),
            "grouped gate/up")
     _check(lib.js_gemm_bf16_grouped(_p(h), _p(dn), _p(ys), T * top_k, H, I, h.stride(0), dn.stride(0), ys.stride(0),
-                                    EPI_STORE, E, _p(group_off), T, None, None, None, None, 1, st, 0, _stream()),
+                                    EPI_STORE, E, _p(group_off), cover, None, None, None, None, 1, st, 0, _stream()),
            "grouped down")
     if on_device and x.dtype == torch.bfloat16:
         # weighted sum of each token's expert outputs in choice order (fixed order, no atomics)

@@ -216,7 +216,7 @@ class TokenShardedEP:
     RING = 6
 
     def __init__(self, group, num_experts: int, top_k: int, hidden: int, max_tokens: int,
-                 rows_factor: float = 4.0):
+                 rows_factor: float = 2.0):
         import torch.distributed as dist
         from ..ops import cuda_ext as X
         from .tp import ring_mod_for
@@ -227,11 +227,13 @@ class TokenShardedEP:
         self.E, self.k, self.H, self.max_tokens = int(num_experts), int(top_k), int(hidden), int(max_tokens)
         self.n_local = self.E // self.world
         self.first = self.rank * self.n_local
-        # receive slab: worst case every pair of every rank lands here; the grouped GEMM launch covers
-        # `max_rows_per_expert` rows per expert (a load beyond it is reported through the status word)
+        # receive slab: worst case every pair of every rank lands here.  The grouped GEMMs are LAUNCHED for
+        # `max_rows_per_expert` rows per expert (a few times the balanced load); an expert that receives more is
+        # still finished: its CTAs walk on through its remaining row tiles, so skewed routing (identical tokens,
+        # pad rows) costs time, never correctness
         self.slab_rows = self.world * self.max_tokens * self.k
         avg = self.slab_rows / self.E
-        self.max_rows_per_expert = int(min(self.slab_rows, ((int(rows_factor * avg) + 128 + 127) // 128) * 128))
+        self.max_rows_per_expert = int(min(self.slab_rows, ((int(rows_factor * avg) + 127) // 128) * 128 or 128))
         dev = "cuda"
         self.slab = SymmetricBuffer(self.slab_rows * self.H * 2, group)
         self.meta = SymmetricBuffer(self.slab_rows * 8, group)

@@ -284,6 +284,44 @@ def test_grouped_moe_matches_reference(ext, T):
     ext.check_status("cuda")
 
 
+@pytest.mark.parametrize("epi", ["store", "swiglu"])
+def test_grouped_gemm_finishes_groups_larger_than_the_launch_covers(ext, epi):
+    """The grouped GEMM is launched for ``max_rows_per_group`` rows per group; a group with more rows is still
+    computed completely (its CTAs walk on through its remaining row tiles), empty groups cost nothing."""
+    import ctypes
+    lib = ext.load()
+    H, N = 256, 256
+    counts = [300, 5, 0, 700, 128, 1]                       # rows per group; the launch covers 128
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+    total, G = off[-1], len(counts)
+    x = rnd(total, H, seed=40)
+    w = rnd(G, N, H, scale=0.05, seed=41)
+    group_off = torch.tensor(off, dtype=torch.int32, device="cuda")
+    out_cols = N // 2 if epi == "swiglu" else N
+    out = torch.full((total, out_cols), float("nan"), dtype=torch.bfloat16, device="cuda")
+    if epi == "swiglu":
+        from jetspec_b200.parallel.ep import interleave_experts
+        wk = interleave_experts(w)                          # (G*N, H): per tile N/2... gate rows then up rows
+    else:
+        wk = w.reshape(G * N, H).contiguous()
+    rc = lib.js_gemm_bf16_grouped(ext._p(x), ext._p(wk), ext._p(out), total, N, H, x.stride(0), wk.stride(0),
+                                  out.stride(0), ext.EPI_SWIGLU if epi == "swiglu" else ext.EPI_STORE, G,
+                                  ext._p(group_off), 128, None, None, None, None, 1,
+                                  ext._p(ext.status_word("cuda")), 0, ext._stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    ext.check_status("cuda")
+    for g in range(G):
+        rows = slice(off[g], off[g + 1])
+        y = x[rows].float() @ w[g].float().t()
+        if epi == "swiglu":
+            y = torch.nn.functional.silu(y[:, :N // 2]) * y[:, N // 2:]
+        if counts[g]:
+            assert rel_err(out[rows], y) < BF16_TOL, f"group {g}"
+
+
 @pytest.mark.parametrize("T,E,k,renorm", [(96, 128, 8, True), (5, 16, 4, False), (1024, 128, 8, True)])
 def test_moe_route_and_sort_kernels(ext, T, E, k, renorm):
     from jetspec_b200.ops import reference as ref

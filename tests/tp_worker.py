@@ -84,6 +84,10 @@ def ep_engine_main(rank, world):
     print(f"[rank {rank}] ep engine: AR ok {ar == want}, random-tree ok {rnd['token_ids'] == want} "
           f"({rnd['rounds']} rounds), oracle-tree ok {orc['token_ids'] == want} ({orc['rounds']} rounds, "
           f"{orc['tpf']:.2f} tokens/round)", flush=True)
+    ep.close()
+    del eng, solo, model
+    torch.cuda.empty_cache()
+    ok &= ep_engine_a3b_geometry(rank, world, dev)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -91,6 +95,39 @@ def ep_engine_main(rank, world):
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if int(flag) == 1 else 1)
+
+
+def ep_engine_a3b_geometry(rank, world, dev) -> bool:
+    """The same check at the layer geometry of Qwen3-30B-A3B (128 experts, top-8, hidden 2048, expert width 768,
+    32 query / 4 KV heads), four layers deep: 128-node trees, a real draft head inside the round graph, an oracle
+    script with a different acceptance profile (hence a different number of rounds) on every rank."""
+    from jetspec_b200 import JetSpecEngine, SamplingParams, OracleTreeDrafter, OracleOverrideDrafter, DraftHeadTreeDrafter
+    from jetspec_b200.models import Qwen3ForCausalLM, Qwen3Config, DraftHeadModel, draft_head_config
+    from jetspec_b200.parallel import TokenShardedEP
+    from jetspec_b200.ops import cuda_ext as X
+    cfg = Qwen3Config(vocab_size=8192, hidden_size=2048, intermediate_size=6144, num_hidden_layers=4,
+                      num_attention_heads=32, num_key_value_heads=4, head_dim=128, num_experts=128,
+                      num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True, model_type="qwen3_moe")
+    model = Qwen3ForCausalLM.random_init(cfg, seed=4, dtype=torch.bfloat16, device="cuda", init="stable")
+    head = DraftHeadModel.random_init(draft_head_config(cfg, num_layers=1, block_size=21, num_taps=3), seed=5,
+                                      dtype=torch.bfloat16, device="cuda")
+    prompt = torch.randint(0, cfg.vocab_size, (1, 300 + 40 * rank), generator=torch.Generator().manual_seed(10 + rank))
+    sp = SamplingParams(0.0, 96)
+    want = [(int(prompt[0, -1]) + 1 + i) % cfg.vocab_size for i in range(96)]
+    ep = TokenShardedEP(None, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, max_tokens=128)
+    eng = JetSpecEngine(model, device=dev, dtype=torch.bfloat16, max_seq_len=1024, expert_parallel=ep)
+    ar = eng.generate(prompt, sp)["token_ids"]
+    oracle = OracleTreeDrafter(prompt[0].tolist() + want, cfg.vocab_size, tree_width=7, mean_accept=3.0 + 2 * rank,
+                               max_accept=19, seed=rank)
+    drafter = OracleOverrideDrafter(DraftHeadTreeDrafter(head, model, block_size=21), oracle)
+    out = eng.generate_tree(prompt, drafter, tree_depth=20, tree_width=7, budget=128, sampling_params=sp,
+                            return_stats=True, session=True)
+    X.check_status("cuda")
+    good = ar == want and out["token_ids"] == want
+    print(f"[rank {rank}] ep engine, A3B layer geometry: AR ok {ar == want}, tree ok {out['token_ids'] == want} "
+          f"({out['rounds']} rounds, {out['tpf']:.2f} tokens/round)", flush=True)
+    ep.close()
+    return good
 
 
 def main():
