@@ -333,13 +333,13 @@ class JetSpecEngine:
         sid = self._new_seq_id()
         try:
             graph_sampling = sp.temperature <= 0.0 or (self.tp is None and self.ep is None)
-            if self.use_kernels and graph_sampling and not extend_kwargs:
+            if self.use_kernels and graph_sampling and not env_flag("JETSPEC_FORCE_EAGER_TREE"):
                 from .fast_round import FastRound
                 fast = FastRound.get(self)
-                if fast.supports_tree(tree_drafter, algo_obj, block_size, tree_width, budget):
+                if fast.supports_tree(tree_drafter, algo_obj, block_size, tree_width, budget, extend_kwargs):
                     return fast.generate_tree(sid, committed, tree_drafter, algo_obj, block_size, tree_width, budget,
                                               taps, sp, return_stats, tree_diag, max_depth, prompt_info, profile_table,
-                                              total)
+                                              total, extend_kwargs=extend_kwargs)
             return self._generate_tree_eager(sid, committed, tree_drafter, algo_obj, algo, algo_kwargs, block_size,
                                              tree_width, budget, taps, sp, return_stats, prompt_info, profile_table,
                                              tree_diag, max_depth, extend_kwargs, total)

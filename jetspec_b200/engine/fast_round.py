@@ -350,10 +350,19 @@ class FastRound:
         self._tp_graph_key = None
 
     # ------------------------------------------------------------------ support matrix
-    def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget) -> bool:
+    def supports_tree(self, drafter, algo_obj, block_size, tree_width, budget, extend_kwargs=None) -> bool:
         cfg = self.cfg
         if cfg.head_dim != 128 or budget > 256 or tree_width > 8 or block_size - 1 > 48:
             return False
+        if extend_kwargs:
+            # the gated extension stays on the graph path for a draft head that runs inside the round, in chain mode
+            head, scripted, host = self._split_drafter(drafter)
+            ext_budget = int(extend_kwargs.get("ext_budget", max(1, block_size - 1)))
+            if (head is None or scripted is not None or host is not None or extend_kwargs.get("mode", "chain") != "chain"
+                    or self.tp is not None or self.ep is not None or ext_budget < 1 or ext_budget > block_size - 1
+                    or block_size - 1 + ext_budget > 48 or budget + ext_budget > 256
+                    or getattr(head.head, "hidden_dim_adapter", None) is not None):
+                return False
         return hasattr(algo_obj, "caps_from_topk")
 
     @staticmethod
@@ -376,12 +385,13 @@ class FastRound:
 
     # ------------------------------------------------------------------ buffers + capture
     def _round(self, NB: int, D: int, K: int, budget: int, head: Optional[DraftHeadTreeDrafter], staged: bool,
-               tap_ids, max_new: int, remote=None, temperature: float = 0.0):
+               tap_ids, max_new: int, remote=None, temperature: float = 0.0, ext=None):
         pool = self.eng.pool
         tap_ids = list(tap_ids) if (tap_ids and (head is not None or remote is not None)) else None
         temperature = float(temperature) if temperature > 0.0 else 0.0
+        ext = (int(ext[0]), float(ext[1])) if ext else None       # (extension budget, gap threshold)
         key = (NB, D, K, budget, id(head) if head is not None else 0, staged, tuple(tap_ids or ()), id(pool),
-               id(remote) if remote is not None else 0, temperature)
+               id(remote) if remote is not None else 0, temperature, ext)
         if key in self.graphs:
             return self.graphs[key]
         if pool.resident():
@@ -422,6 +432,14 @@ class FastRound:
                       "idx": torch.zeros(NB, nt, dtype=torch.int32, device=dev)}
         r["am_val"] = torch.zeros(NB, dtype=torch.float32, device=dev)
         r["temperature"] = temperature
+        r["ext"] = ext
+        if ext is not None:
+            # gated chain extension: the round is captured as three graphs (draft + build + gate | conditioned draft
+            # pass + splice | verify + accept) with one extra host read of the gate between the first two
+            r["gate"] = _i32(4, dev)
+            r["gate_host"] = torch.zeros(4, dtype=torch.int32).pin_memory()
+            r["ext_tok"] = _i32(max(1, Dn), dev)
+            r["ext_val"] = torch.zeros(max(1, Dn), dtype=torch.float32, device=dev)
         if temperature > 0.0:
             # sampling keeps the round in the graph: the LM head writes fp32 logits for the NB nodes, one kernel
             # draws a token per node (inverse CDF, uniforms from the graph-registered generator), and acceptance
@@ -447,10 +465,17 @@ class FastRound:
         if par is not None:
             par.begin_sequence(par._turn)     # cycle length that is safe across replays
             r["ring_mod"] = par.ring_mod
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self._launch_round(r, pdl=_PDL)
-        r["graph"] = g
+        if ext is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch_round(r, pdl=_PDL)
+            r["graph"] = g
+        else:
+            for part in ("a", "x", "b"):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._launch_round(r, pdl=_PDL, part=part)
+                r["graph_" + part] = g
         pool.frozen = True
         self.graphs[key] = r
         self.launches_per_round = r["launches"]
@@ -492,6 +517,9 @@ class FastRound:
         d["topk_tok"] = _i32(Dd * K, dev).view(Dd, K)
         d["topk_lp"] = torch.zeros(Dd, K, dtype=torch.float32, device=dev)
         d["freq"] = X.inv_freq(hc.head_dim, hc.rope_theta, dev)
+        nt_full = X.n_tiles(head._fwd.lm_head_w.shape[0])
+        d["ext_ws"] = {"val": torch.zeros(Dd, nt_full, dtype=torch.float32, device=dev),
+                       "idx": torch.zeros(Dd, nt_full, dtype=torch.int32, device=dev)}
         r["draft"] = d
 
     @staticmethod
@@ -557,12 +585,21 @@ class FastRound:
                                           max(1, r["K"]), d["tk_ws"], d["topk_tok"], d["topk_lp"], pdl=pdl)
         return n + 3
 
-    def _launch_round(self, r, pdl: bool, use_remote: bool = True) -> int:
+    def _launch_round(self, r, pdl: bool, use_remote: bool = True, part: str = "all") -> int:
+        """Launch the kernels of one round.  ``part``: ``"all"`` (one graph), or for rounds with the gated tree
+        extension ``"a"`` (draft, caps, tree build, extension gate), ``"x"`` (path-conditioned draft pass + splice)
+        and ``"b"`` (verify forward, acceptance, commit)."""
         lib, p, s = X.load(), X._p, X._stream
         pool, cfg = self.eng.pool, self.cfg
         NB, D, K = r["NB"], r["D"], r["K"]
         status = X.status_word(self.device)
         n = 0
+        if part == "all" and r.get("ext") is not None:      # the warm-up run of an extension round: every part once
+            return sum(self._launch_round(r, pdl, use_remote, q) for q in ("a", "x", "b"))
+        if part == "x":
+            return self._launch_extension(r, pdl)
+        if part == "b":
+            return self._launch_verify(r, pdl, use_remote)
         if r["head"] is not None and D > 0:
             n += self._launch_draft(r, pdl)
             if not r["staged"]:
@@ -586,12 +623,59 @@ class FastRound:
                                    r["W"], p(r["committed"]), p(r["state"]), p(pool.slot_map), p(r["seq_rows"]),
                                    pool.max_seq_len, p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["positions"]),
                                    p(r["slots"]), p(r["mask"]), p(status), int(pdl), s()), "js_tree_build")
+        if part == "a":
+            ext_budget, gap = r["ext"]
+            lib.js_tree_ext_gate.restype = ctypes.c_int
+            X._check(lib.js_tree_ext_gate(p(r["tokens"]), p(r["parents"]), p(r["state"]), p(r["topk_tok"]), p(r["topk_lp"]),
+                                          D, max(1, K), ctypes.c_float(gap), ext_budget, NB, p(r["gate"]), int(pdl), s()),
+                     "js_tree_ext_gate")
+            r["gate_host"].copy_(r["gate"], non_blocking=True)
+            return n + 2
+        return n + 1 + self._launch_verify(r, pdl, use_remote)
+
+    def _launch_extension(self, r, pdl: bool) -> int:
+        """The path-conditioned draft pass (the block reads [anchor, rank-1 chain tokens]) and the splice of its
+        first ``ext`` argmax tokens as a chain below the leaf the gate found (reference: ``_maybe_extend_tree``,
+        ``jetspec/inference_engine/engine.py:109-146``, chain mode of ``jetspec/tree/_core/extend.py:100-129``)."""
+        lib, p, s = X.load(), X._p, X._stream
+        head, d = r["head"], r["draft"]
+        hm, hc = head.head, head.head.config
+        bs, D, K, NB = d["bs"], r["D"], max(1, r["K"]), r["NB"]
+        ext_budget = r["ext"][0]
+        lib.js_draft_prep_fill.restype = ctypes.c_int
+        X._check(lib.js_draft_prep_fill(p(r["state"]), p(r["committed"]), int(hm.mask_token_id), bs, bs, bs,
+                                        p(d["block_ids"]), p(d["block_pos"]), p(d["ctx_pos"]), p(d["n_new"]),
+                                        p(r["topk_tok"]), K, D, int(pdl), s()), "js_draft_prep_fill")
+        st = d["stack"]
+        X.embed(d["block_ids"], head._fwd.embed_w, out=st.x, pdl=pdl)
+        causal = hm.resolve_causal_head("auto")
+        n = 2 + decoder_layers(hc, d["layers"], st, d["k"], d["v"], d["slot_map"], d["seq_rows"], d["cu_q"],
+                               r["state"][ST_CTX:ST_CTX + 1], d["block_pos"], d["block_pos"],
+                               None if causal else d["full_mask"], causal, d["freq"], pdl=pdl)
+        X.rmsnorm(st.x, hm.norm.weight, hc.rms_norm_eps, out=d["hn"], pdl=pdl)
+        rows = d["hn"][:bs - 1] if head.draft_shift else d["hn"][1:bs]
+        X.lm_head_argmax(rows[:ext_budget], head._fwd.lm_head_w, pdl=pdl, out_idx=r["ext_tok"][:ext_budget],
+                         out_val=r["ext_val"][:ext_budget], ws=d["ext_ws"])
+        lib.js_tree_ext_splice.restype = ctypes.c_int
+        X._check(lib.js_tree_ext_splice(p(r["tokens"]), p(r["parents"]), p(r["depth"]), p(r["positions"]), p(r["mask"]),
+                                        p(r["state"]), p(r["gate"]), p(r["ext_tok"]), ext_budget, NB, r["W"],
+                                        p(X.status_word(self.device)), int(pdl), s()), "js_tree_ext_splice")
+        return n + 4
+
+    def _launch_verify(self, r, pdl: bool, use_remote: bool = True) -> int:
+        """Verify forward over the round's tree, greedy (or sampled) tokens, acceptance and commit."""
+        lib, p, s = X.load(), X._p, X._stream
+        pool, cfg = self.eng.pool, self.cfg
+        NB = r["NB"]
+        status = X.status_word(self.device)
+        remote = r.get("remote") if use_remote else None
+        n = 0
         st = r["stack"]
         pf = self.prefetcher
         if pf is not None:
             pf.ahead(self.layers[0]["qkv"])       # the first projection's weights arrive during the tree build
         X.embed(r["tokens"], self.embed_w, out=st.x, pdl=pdl)
-        n += 2 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
+        n += 1 + decoder_layers(self.lcfg, self.layers, st, pool.k_pool, pool.v_pool, pool.slot_map, r["seq_rows"],
                                 r["cu_q"], r["state"][ST_PAST:ST_PAST + 1], r["positions"], r["slots"], r["mask"],
                                 False, self.freq, taps=r["taps"], tap_ids=r["tap_ids"], pdl=pdl, tp=self.tp,
                                 prefetch=pf, then_prefetch=self.lm_head_w, final_norm=(self.final_norm, r["xn"]),
@@ -893,10 +977,15 @@ class FastRound:
     # ------------------------------------------------------------------ public entry points
     @torch.inference_mode()
     def generate_tree(self, sid, committed, tree_drafter, algo_obj, block_size, tree_width, budget, taps, sp,
-                      return_stats, tree_diag, max_depth, prompt_info, profile_table, total):
+                      return_stats, tree_diag, max_depth, prompt_info, profile_table, total, extend_kwargs=None):
         from .engine import bucket_for_n
         eng = self.eng
-        D, K, NB = max(1, block_size - 1), int(tree_width), bucket_for_n(budget)
+        ext = None
+        if extend_kwargs:
+            ext = (int(extend_kwargs.get("ext_budget", max(1, block_size - 1))),
+                   float(extend_kwargs.get("gap_threshold", 1.0)))
+        D, K = max(1, block_size - 1), int(tree_width)
+        NB = bucket_for_n(budget + (ext[0] if ext else 0))
         from .disagg import RemoteDraftHead
         remote = None
         if isinstance(tree_drafter, RemoteDraftHead):
@@ -914,13 +1003,16 @@ class FastRound:
             # take the eager path
             return eng._generate_tree_eager(sid, committed, tree_drafter, algo_obj, algo_obj.name, None, block_size,
                                             tree_width, budget, taps, sp, return_stats, prompt_info, profile_table,
-                                            tree_diag, max_depth, None, total)
+                                            tree_diag, max_depth, extend_kwargs, total)
         if head is not None:
             taps = list(head.target_layer_ids) if taps is None else taps
             if head.block_size != block_size:
                 raise ValueError(f"draft head block_size {head.block_size} != block_size {block_size}")
+        if ext is not None and D + ext[0] > max_depth:
+            raise ValueError(f"tree depth {D + ext[0]} exceeds max_tree_depth {max_depth}; "
+                             "raise max_tree_depth when extending trees")
         r = self._round(NB, D, K, budget, head, staged, taps, sp.max_new_tokens, remote=remote,
-                        temperature=sp.temperature)
+                        temperature=sp.temperature, ext=ext)
         if plan is not None:
             self._stage_caps_plan(r, plan, D, K)
         first = self._begin(r, sid, committed, taps if (head is not None or remote is not None) else None, total,
@@ -937,6 +1029,7 @@ class FastRound:
         events = []
         frozen = None                      # expert parallelism: device state a finished rank keeps replaying from
         final_len = None
+        extended = 0
         while True:
             active = len(new_ids) < sp.max_new_tokens and not done
             if not active:
@@ -967,13 +1060,21 @@ class FastRound:
                 stage_caps[:] = np.asarray(algo_obj.caps_from_topk(lp_l, K, prompt_info=prompt_info,
                                                                    profile_table=profile_table), dtype=np.int32)
             if self.timing:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0 = torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
+            if ext is None:
                 r["graph"].replay()
+            else:         # draft + build + gate, one host read, then (if the gate fired) the conditioned pass + splice
+                r["graph_a"].replay()
+                stream.synchronize()
+                if int(r["gate_host"][0]) != 0:
+                    r["graph_x"].replay()
+                    extended += 1
+                r["graph_b"].replay()
+            if self.timing:
+                e1 = torch.cuda.Event(enable_timing=True)
                 e1.record(stream)
                 events.append((e0, e1))
-            else:
-                r["graph"].replay()
             stream.synchronize()
             if active:
                 rounds += 1
@@ -1014,6 +1115,8 @@ class FastRound:
                "tpf": (len(new_ids) / rounds if rounds else 0.0)}
         if return_stats:
             out.update(accept_lengths=accept_lengths, tree_sizes=tree_sizes, rounds=rounds)
+            if ext is not None:
+                out["extended_rounds"] = extended
         if depth_hist is not None:
             out["tree_nodes_per_depth"] = depth_hist
         return out

@@ -311,6 +311,42 @@ def test_sampling_stays_on_the_graph_path(stable_engine, prompt, monkeypatch):
     cuda_ext.check_status("cuda")
 
 
+def test_tree_extension_stays_on_the_graph_path(stable_engine, prompt, monkeypatch):
+    """Gated chain extension with an in-graph draft head: three captured segments (draft + build + gate, conditioned
+    pass + splice, verify + accept) instead of the eager loop; lossless, the same tree sizes as the eager path, and
+    a gate that never fires leaves the trees at the plain budget."""
+    from jetspec_b200 import SamplingParams, DraftHeadTreeDrafter
+    from jetspec_b200.models import DraftHeadModel, draft_head_config
+    model = stable_engine.model
+    hcfg = draft_head_config(model.config, num_layers=1, block_size=7, num_taps=3)
+    head = DraftHeadModel.random_init(hcfg, seed=5, dtype=torch.bfloat16, device="cuda")
+    sp = SamplingParams(0.0, 20)
+    expect = [(int(prompt[0, -1]) + 1 + i) % 4096 for i in range(20)]
+    kw = dict(tree_depth=6, tree_width=3, budget=24, sampling_params=sp, return_stats=True, max_tree_depth=10,
+              target_layer_ids=head.target_layer_ids)
+    always = {"gap_threshold": -1e9, "ext_budget": 4, "mode": "chain"}
+    eager = stable_engine._generate_tree_eager
+    calls = {"n": 0}
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return eager(*a, **k)
+    monkeypatch.setattr(stable_engine, "_generate_tree_eager", counting)
+    out = stable_engine.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=7), extend_kwargs=always, **kw)
+    assert calls["n"] == 0                                   # the graph path took it
+    assert out["token_ids"] == expect
+    assert out["extended_rounds"] == out["rounds"] and set(out["tree_sizes"]) == {28}      # 24 + 4 every round
+    never = stable_engine.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=7),
+                                        extend_kwargs={"gap_threshold": 1e9, "ext_budget": 4}, **kw)
+    assert never["token_ids"] == expect and never["extended_rounds"] == 0 and set(never["tree_sizes"]) == {24}
+    # the eager loop (what a subtree-mode request still takes) builds trees of the same sizes
+    monkeypatch.setenv("JETSPEC_FORCE_EAGER_TREE", "1")
+    ref = stable_engine.generate_tree(prompt, DraftHeadTreeDrafter(head, model, block_size=7), extend_kwargs=always, **kw)
+    assert calls["n"] == 1 and ref["token_ids"] == expect and set(ref["tree_sizes"]) == {28}
+    from jetspec_b200.ops import cuda_ext
+    cuda_ext.check_status("cuda")
+
+
 def test_session_reuses_graph(engine, prompt):
     from jetspec_b200 import SamplingParams, RandomTreeDrafter
     from jetspec_b200.engine.fast_round import FastRound
