@@ -6,6 +6,7 @@ round (cold weights, no host gaps), unlike a single launch between two events.
 
     python bench/gemm_chain.py                 # the four decoder shapes of Qwen3-8B at 128 rows, all configurations
     M=21 ONLY=qkv,down python bench/gemm_chain.py
+    SHARDS=4 python bench/gemm_chain.py        # the same layer as one rank of a tensor-parallel job of 4 sees it
 """
 import json
 import os
@@ -45,7 +46,10 @@ def main():
     X.load()
     M = int(os.environ.get("M", 128))
     only = os.environ.get("ONLY")
-    for name, N, K, epi in SHAPES:
+    shards = int(os.environ.get("SHARDS", 1))       # column-parallel qkv / gate-up, row-parallel o / down
+    shapes = [(n, N // shards if n in ("qkv", "gu") else N, K if n in ("qkv", "gu") else K // shards, e)
+              for n, N, K, e in SHAPES]
+    for name, N, K, epi in shapes:
         if only and name not in only.split(","):
             continue
         size = N * K * 2
@@ -57,14 +61,15 @@ def main():
         res = {"cublas": round(chain_time(lambda i: torch.matmul(x, ws[i].t(), out=full), R), 1),
                "picked": round(chain_time(lambda i: X.gemm(x, ws[i], out=out, epi=epi, pdl=True), R), 1)}
         for deep in ((0, 2, 1) if not os.environ.get("PICKED_ONLY") else ()):
-            for split in (1, 2, 3, 4):
-                for pdl in (0, 1):
-                    try:
-                        t = chain_time(lambda i: X.gemm(x, ws[i], out=out, epi=epi, bn=128, split=split, deep=deep,
-                                                        pdl=bool(pdl)), R)
-                    except Exception:
-                        continue
-                    res[f"budget{deep}_split{split}_pdl{pdl}"] = round(t, 1)
+            for bn in (128, 256):
+                for split in (1, 2, 3, 4, 6, 8):
+                    for pdl in ((0, 1) if bn == 128 else (1,)):
+                        try:
+                            t = chain_time(lambda i: X.gemm(x, ws[i], out=out, epi=epi, bn=bn, split=split, deep=deep,
+                                                            pdl=bool(pdl)), R)
+                        except Exception:
+                            continue
+                        res[f"bn{bn}_budget{deep}_split{split}_pdl{pdl}"] = round(t, 1)
         X.check_status("cuda")
         print(json.dumps({"shape": name, "M": M, "N": N, "K": K, "ideal_us_at_measured_copy_bw": round(size / HBM_GBS / 1e3, 1),
                           "picked_config": X.pick_gemm_config(M, N, K, epi), "us": res}), flush=True)

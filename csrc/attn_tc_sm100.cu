@@ -32,6 +32,12 @@ constexpr int kStageKV = 2 * TKEYS * 256;      // K then V, each 2 halves x 64 k
 constexpr int kSmemQ = TROWS * 256;            // 2 halves x 128 rows x 128 B
 constexpr int kSmemP = TROWS * 128;            // 128 rows x 64 keys bf16
 constexpr int kAttnTcSmem = kSmemQ + TSTAGES * kStageKV + 2 * kSmemP + 256 + 1024;
+// Key splits that merge inside a cluster (portable cluster size); the chunk receive area must fit the dead
+// K/V stages + P buffers, the (max, sum) pairs the dead Q tile.
+constexpr int kMaxClusterSplits = 8;
+static_assert(kMaxClusterSplits * 16384 <= TSTAGES * kStageKV + 2 * kSmemP, "chunk receive area");
+static_assert(3 * 2 * 16384 <= TSTAGES * kStageKV + 2 * kSmemP, "chunk receive area, 3 splits own 2 chunks each");
+static_assert(kMaxClusterSplits * TROWS * 8 <= kSmemQ, "(max, sum) receive area");
 
 struct AttnTcParams {
   const __nv_bfloat16* q;      // (T, Hq, 128)
@@ -467,10 +473,11 @@ __global__ void __launch_bounds__(TTHREADS, 1) paged_tree_attn_tc_kernel(AttnTcP
     // ---------------------------------------------------------------- merge of the key splits inside the cluster
     // Column chunk c (32 of the 128 output columns) is finished by CTA c % splits.  Every CTA pushes its
     // unnormalised chunk (column-major, 16 KB) into the owner's shared memory and its rows' (max, sum) to
-    // all CTAs; the receive area reuses the K/V stages, which are dead once every CTA has left its main loop.
+    // all CTAs; the receive areas reuse the K/V stages + P buffers (chunks, at most 8 x 16 KB = 128 KB) and the
+    // Q tile ((max, sum) pairs, at most 8 KB), all dead once every CTA of the cluster has left its main loop.
     const int per_owner = (4 + p.splits - 1) / p.splits;
     float* recv_o = reinterpret_cast<float*>(sKV);
-    float* recv_ml = recv_o + p.splits * per_owner * 4096;
+    float* recv_ml = reinterpret_cast<float*>(sQ);
     tc_fence_before();
     __syncthreads();
     cluster_sync();
@@ -581,6 +588,38 @@ extern "C" int js_attn_tc_set_trace(unsigned long long* buf) {
 
 extern "C" int js_attn_merge(float* ws_o, float* ws_ml, void* out, int T, int Hq, int splits, int pdl, cudaStream_t stream);
 
+// How many clusters of `splits` CTAs of the kernel for GQA group size G can be resident at once on the current
+// device (a cluster lives inside one GPC, so this is less than SMs / splits); 0 or negative = cannot say.  The host
+// picks the number of key splits from it so that a launch is one wave.
+extern "C" int js_attn_tc_max_active_clusters(int G, int splits) {
+  using namespace js;
+  if (splits < 1 || splits > kMaxClusterSplits) return -1;
+  const void* kern = nullptr;
+  switch (G) {
+    case 1: kern = reinterpret_cast<const void*>(paged_tree_attn_tc_kernel<1>); break;
+    case 2: kern = reinterpret_cast<const void*>(paged_tree_attn_tc_kernel<2>); break;
+    case 4: kern = reinterpret_cast<const void*>(paged_tree_attn_tc_kernel<4>); break;
+    case 8: kern = reinterpret_cast<const void*>(paged_tree_attn_tc_kernel<8>); break;
+    case 16: kern = reinterpret_cast<const void*>(paged_tree_attn_tc_kernel<16>); break;
+    default: return -2;
+  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnTcSmem) != cudaSuccess) return -3;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, splits);
+  cfg.blockDim = dim3(TTHREADS);
+  cfg.dynamicSmemBytes = kAttnTcSmem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return -4; }
+  return n;
+}
+
 // Same arguments as js_paged_tree_attention.  Needs 128 % (Hq / Hkv) == 0 and W <= 8 (windows of up to 256 nodes).
 extern "C" int js_paged_tree_attention_tc(const void* q, const void* k_pool, const void* v_pool, const int* slot_map,
                                           const int* seq_rows, const int* cu_q, const int* past_lens,
@@ -594,10 +633,28 @@ extern "C" int js_paged_tree_attention_tc(const void* q, const void* k_pool, con
   if (splits < 1) return -11;
   if (splits > 1 && (ws_o == nullptr || ws_ml == nullptr)) return -12;
   if (!causal && (mask_bits == nullptr || W < 1 || W > 8)) return -13;
+  // The key splits merge inside a cluster only while every cluster of the launch is resident at once (a second
+  // wave would double the kernel's time); otherwise partials go through the workspace and the merge kernel.
+  bool in_cluster = splits >= 2 && splits <= kMaxClusterSplits;
+  if (in_cluster) {
+    static int room[kMaxDevicesCached][5][kMaxClusterSplits + 1] = {};     // 0 = not asked yet
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int gi = G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : G == 8 ? 3 : 4;
+    int r = 0;
+    if (dev >= 0 && dev < kMaxDevicesCached) r = room[dev][gi][splits];
+    if (r == 0) {
+      r = js_attn_tc_max_active_clusters(G, splits);
+      if (r <= 0) r = -1;
+      if (dev >= 0 && dev < kMaxDevicesCached) room[dev][gi][splits] = r;
+    }
+    const int npt = 128 / G;
+    in_cluster = r > 0 && ((T + npt - 1) / npt) * Hkv <= r;
+  }
   AttnTcParams p{reinterpret_cast<const __nv_bfloat16*>(q), reinterpret_cast<const __nv_bfloat16*>(k_pool),
                  reinterpret_cast<const __nv_bfloat16*>(v_pool), slot_map, seq_rows, cu_q, past_lens, mask_bits,
                  reinterpret_cast<__nv_bfloat16*>(out), ws_o, ws_ml, status, B, T, Hq, Hkv, S, max_len, W, causal,
-                 splits, scale * 1.4426950408889634f, (splits == 2 || splits == 4) ? 1 : 0};
+                 splits, scale * 1.4426950408889634f, in_cluster ? 1 : 0};
   int rc;
   switch (G) {
     case 1: rc = launch_attn_tc<1>(p, (T + 127) / 128 + B, pdl != 0, stream); break;

@@ -210,8 +210,9 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
     scale, eps = 1.0 / math.sqrt(D), cfg.rms_norm_eps
     last = len(layers) - 1
     n = 0
-    # the split merge is a second launch unless the tcgen05 kernel does it inside a cluster (2 or 4 splits)
-    in_kernel = X.attn_impl(Hq, Hkv, 0 if mask_bits is None else mask_bits.shape[1]) == "tc" and st.splits in (2, 4)
+    # the split merge is a second launch unless the tcgen05 kernel does it inside a cluster
+    in_kernel = (X.attn_impl(Hq, Hkv, 0 if mask_bits is None else mask_bits.shape[1]) == "tc"
+                 and X.attn_merges_in_cluster(st.T, Hq, Hkv, st.splits))
     merge_launch = 1 if st.splits > 1 and not in_kernel else 0
     fuse_norm = tp is not None and tp.push_only >= 2     # the all-reduce tail computes the following norm
     h_ready = False                                      # st.h already holds this layer's normalised input

@@ -485,6 +485,7 @@ def attn_splits(q_tiles: int, Hkv: int, max_keys: int) -> int:
     return max(1, min(want, (max_keys + 127) // 128, 16))
 
 
+ATTN_CLUSTER_SPLITS = 8       # key splits the tcgen05 kernel merges inside one cluster (kMaxClusterSplits)
 ATTN_IMPL = os.environ.get("JETSPEC_ATTN", "tc")     # "tc": tcgen05 kernel where it applies; "mma": mma.sync kernel
 
 
@@ -493,10 +494,43 @@ def attn_impl(Hq: int, Hkv: int, W: int = 0) -> str:
     return "tc" if ATTN_IMPL == "tc" and 128 % G == 0 and W <= 8 else "mma"
 
 
+_ATTN_ROOM: dict = {}
+
+
+def _attn_cluster_room(G: int, splits: int) -> int:
+    """Clusters of ``splits`` CTAs of the tcgen05 attention kernel the current device holds at once."""
+    dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    key = (dev, G, splits)
+    if key not in _ATTN_ROOM:
+        n = 0
+        if dev >= 0:
+            lib = load()
+            lib.js_attn_tc_max_active_clusters.restype = ctypes.c_int
+            n = int(lib.js_attn_tc_max_active_clusters(int(G), int(splits)))
+        if n <= 0:       # no device / no answer: what was measured on a 148-SM part, else a conservative guess
+            n = {2: 72, 3: 40, 4: 32}.get(splits, SM_COUNT // (splits + 2))
+        _ATTN_ROOM[key] = n
+    return _ATTN_ROOM[key]
+
+
+def attn_merges_in_cluster(T: int, Hq: int, Hkv: int, splits: int) -> bool:
+    """Whether the tcgen05 kernel merges ``splits`` key splits itself (they form one cluster and exchange partial
+    outputs through distributed shared memory): up to ATTN_CLUSTER_SPLITS, and only while all clusters of the
+    launch are resident at once (a cluster lives inside one GPC: 148 SMs hold 33 clusters of 4 but only 15 of 8)."""
+    G = Hq // Hkv
+    if attn_impl(Hq, Hkv) != "tc" or not 2 <= splits <= ATTN_CLUSTER_SPLITS:
+        return False
+    npt = 128 // G
+    return ((T + npt - 1) // npt) * Hkv <= _attn_cluster_room(G, splits)
+
+
 def attn_splits_for(T: int, Hq: int, Hkv: int, max_keys: int) -> int:
     """Key splits for ``T`` query tokens: fill the SMs with ONE wave of CTAs, a couple of key tiles per split."""
     G = Hq // Hkv
     if attn_impl(Hq, Hkv) == "tc":                      # 128 rows per CTA, one CTA per SM
+        # one wave of CTAs, a couple of key tiles per split.  Measured on the decode round (prefix ~2.5 k keys): more,
+        # shorter splits win even when they need the separate merge launch (TP=2: 9 splits + merge 4.60 ms per round,
+        # 6 splits merged inside a cluster 4.71 ms), because the kernel's time is the chain of key tiles of one CTA.
         npt = 128 // G
         ctas = max(1, ((T + npt - 1) // npt) * Hkv)
         return max(1, min(SM_COUNT // ctas, (max_keys + 127) // 128, 16))
