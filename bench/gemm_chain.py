@@ -70,6 +70,12 @@ def main():
                         except Exception:
                             continue
                         res[f"bn{bn}_budget{deep}_split{split}_pdl{pdl}"] = round(t, 1)
+        if M >= 512 and not os.environ.get("PICKED_ONLY"):      # two row tiles per CTA (256 x 256 per CTA)
+            try:
+                res["bn256_two_row_tiles_pdl1"] = round(chain_time(
+                    lambda i: X.gemm(x, ws[i], out=out, epi=epi, bn=256, split=1, deep=3, pdl=True), R), 1)
+            except Exception:
+                pass
         X.check_status("cuda")
         print(json.dumps({"shape": name, "M": M, "N": N, "K": K, "ideal_us_at_measured_copy_bw": round(size / HBM_GBS / 1e3, 1),
                           "picked_config": X.pick_gemm_config(M, N, K, epi), "us": res}), flush=True)

@@ -105,9 +105,11 @@ JS_DEVICE unsigned long long gtime() {
 // BUDGET_KB bounds the pipeline's shared memory: ~96 KB lets two CTAs share an SM (more tiles
 // in flight, natural load balance when the tile count is not a multiple of 148), ~192 KB gives
 // one CTA per SM a deeper pipeline.
-template <int BN, int BUDGET_KB, bool FP4 = false>
+// MT = row tiles per CTA (1 or 2): with 2, one CTA computes a 256 x BN tile as two 128-row accumulators that share
+// every weight stage, so a k-block brings 1.5x the FLOPs per byte through the L2-to-SM path (many-row GEMMs).
+template <int BN, int BUDGET_KB, bool FP4 = false, int MT = 1>
 struct GemmSmem {
-  static constexpr int kStageA = BM * BK * 2;      // 128-byte rows in both modes
+  static constexpr int kStageA = MT * BM * BK * 2; // 128-byte rows in both modes
   static constexpr int kStageW = BN * BK * 2;
   static constexpr int kStageSF = FP4 ? 2048 + (BN / 128) * 2048 : 0;   // 4 scale tiles of A + 4 per 128 rows of W
   static constexpr int kStage = kStageA + kStageW + kStageSF;
@@ -134,14 +136,16 @@ __host__ __device__ inline bool recv_aliases_stages(int tiles_bytes, int recv_to
   return recv_total > 0 && tiles_bytes + recv_total + 1280 > 227 * 1024;
 }
 
-template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
-__global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB, FP4>::kMinBlocks)
+template <int BN, int EPI, int BUDGET_KB, bool FP4 = false, int MT = 1>
+__global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB, FP4, MT>::kMinBlocks)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, GemmParams p) {
-  using S = GemmSmem<BN, BUDGET_KB, FP4>;
+  using S = GemmSmem<BN, BUDGET_KB, FP4, MT>;
   constexpr int kStages = S::kStages;
   static_assert(!FP4 || BN == 128, "the NVFP4 path is built for 128-column tiles");
+  static_assert(MT == 1 || (MT == 2 && !FP4 && BN == 256), "two row tiles per CTA: bf16, 256-column tiles, no K split");
   // FP4: accumulator in columns [0,128), block scales of stage s in [128 + 32 s, 128 + 32 s + 32)
-  constexpr uint32_t kTmemCols = FP4 ? 256 : (BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256);   // power of two
+  // MT == 2: the second row tile's accumulator sits in columns [BN, 2 BN)
+  constexpr uint32_t kTmemCols = MT == 2 ? 512 : FP4 ? 256 : (BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256);   // power of two
   constexpr int kXStep = FP4 ? 128 : BK;              // TMA x advance per k-block (bytes resp. bf16 elements)
   constexpr int kKPerBlock = FP4 ? 256 : BK;          // K elements per pipeline stage
 
@@ -172,7 +176,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bx = lin / static_cast<int>(gridDim.y);
   }
   const int n0 = bx * BN;
-  const int m_first = grouped ? p.group_off[expert] + by * BM : by * BM;
+  const int m_first = grouped ? p.group_off[expert] + by * BM : by * BM * MT;
   const int m_end = grouped ? p.group_off[expert + 1] : p.M;
   const int wn0 = expert * p.N + n0;         // row of this tile in the (stacked) weight matrix
   if (m_first >= m_end) return;              // this expert has fewer row tiles (uniform for the CTA)
@@ -237,7 +241,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i) {
-        tma_load_2d(smem + i * S::kStage, &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(smem + i * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0 + mt * BM);
         load_sfa(i, kb_begin + i);
       }
       bool p_ok = true;
@@ -252,7 +258,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           mbar_expect_tx(&full_bar[s], S::kStage);
           tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * kXStep, wn0);
-          tma_load_2d(smem + s * S::kStage, &tmA, &full_bar[s], (kb_begin + i) * kXStep, m_tile);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d(smem + s * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[s], (kb_begin + i) * kXStep, m_tile + mt * BM);
           load_sfw(s, kb_begin + i);
           load_sfa(s, kb_begin + i);
         }
@@ -299,6 +307,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K by 16 elements = 32 bytes inside the swizzle row = +2 in 16-byte units
             umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+            if constexpr (MT == 2) {     // second row tile: its own A rows and accumulator, the same weight stage
+              const uint64_t a2_desc = umma_desc_sw128(smem_u32(smem + s * S::kStage + BM * BK * 2));
+              umma_f16(tmem_base + BN, a2_desc + 2 * k, b_desc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+            }
           }
         }
         umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
@@ -312,7 +324,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool epi_warp = warp >= 2;
   const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
   const int row = quad * 32 + lane;              // row of the tile owned by this thread
-  const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+  uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
   // split-K: this CTA's receive area (after the pipeline stages) and the chunk -> owner mapping
   constexpr bool kSwiglu = (EPI == EPI_SWIGLU);
   constexpr int kHC = (kSwiglu ? BN / 2 : BN) / 32;          // owned-chunk index space
@@ -324,12 +336,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto local_of = [&](int ch) { return (ch % kHC) / split + (ch >= kHC ? per_owner : 0); };
   bool acc_ok = true;
 
-  for (int tj = 0; tj < n_tiles_cta; ++tj) {     // one pass, except for a grouped-mode expert with many rows
+  // One pass, except: a grouped-mode expert with many rows (the accumulator is reused tile after tile), and the two
+  // row tiles of an MT == 2 CTA (two accumulators, both complete when accum_bar fires once).
+  const int n_epi = MT == 2 ? (m_first + BM < m_end ? 2 : 1) : n_tiles_cta;
+  for (int tj = 0; tj < n_epi; ++tj) {
   m0 = m_first + tj * tile_step;
+  if constexpr (MT == 2) t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(tj * BN);
   const int grow = m0 + row;
   if (epi_warp) {
     pdl_wait();   // residual / C may be produced by the previous kernel
-    acc_ok = mbar_wait(accum_bar, tj & 1, p.status, kTimeoutAccum);
+    if (MT == 1 || tj == 0) acc_ok = mbar_wait(accum_bar, tj & 1, p.status, kTimeoutAccum);
     tc_fence_after();
     if (threadIdx.x == 64) JS_TRACE(3);   // accumulator complete
   }
@@ -828,7 +844,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   }
-  if (tj + 1 < n_tiles_cta && epi_warp) {        // hand the accumulator back for the CTA's next row tile
+  if (MT == 1 && tj + 1 < n_tiles_cta && epi_warp) {        // hand the accumulator back for the CTA's next row tile
     tc_fence_before();
     epi_barrier();
     if (threadIdx.x == 64) mbar_arrive(tmem_free);
@@ -891,12 +907,13 @@ static int make_map_u8(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int BN, int EPI, int BUDGET_KB, bool FP4 = false>
+template <int BN, int EPI, int BUDGET_KB, bool FP4 = false, int MT = 1>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
                        cudaStream_t stream, int groups = 0, int group_m_tiles = 0) {
-  using S = GemmSmem<BN, BUDGET_KB, FP4>;
+  using S = GemmSmem<BN, BUDGET_KB, FP4, MT>;
   static int configured[kMaxDevicesCached] = {};
-  auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4>;
+  auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4, MT>;
+  if (MT != 1 && (split != 1 || groups > 0)) return -19;
   const int recv_total = recv_bytes(split, BN, EPI == EPI_SWIGLU);
   const int data_bytes = recv_aliases_stages(S::kTiles, recv_total) ? (S::kTiles > recv_total ? S::kTiles : recv_total)
                                                                      : S::kTiles + recv_total;
@@ -904,7 +921,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   if (smem_bytes > 227 * 1024) return -18;
   if (ensure_dyn_smem(kern, smem_bytes, configured) != 0) return -3;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, split);
+  cfg.gridDim = dim3((p.N + BN - 1) / BN, (p.M + BM * MT - 1) / (BM * MT), split);
   if (groups > 0) cfg.gridDim = dim3((p.N + BN - 1) / BN, group_m_tiles, groups);   // z = expert, no K split
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem_bytes;
@@ -930,7 +947,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
 
 // C = A[M,K] * W[N,K]^T.  epi: 0 store(+residual) 1 swiglu 2 argmax partials 3 top-8 + lse partials 4 fp32 store.
 // bn in {64,128,256} (SwiGLU also 192: 128 tiles of a 24576-wide gate/up fill one wave); split = K-split cluster size (1..4; store/swiglu only); deep selects the pipeline's
-// shared-memory budget: 0 = 96 KB (two CTAs per SM), 2 = 128 KB, 1 = 192 KB (one CTA per SM).
+// shared-memory budget: 0 = 96 KB (two CTAs per SM), 2 = 128 KB, 1 = 192 KB (one CTA per SM), 3 = 192 KB with two
+// 128-row tiles per CTA sharing each weight stage (bn 256, no split).
 // Returns 0 or a negative code.
 extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* residual, int M, int N, int K, int lda,
                             int ldw, int ldc, int epi, int bn, int split, int deep, float* part_val, int* part_idx,
@@ -953,6 +971,12 @@ extern "C" int js_gemm_bf16(const void* A, const void* W, void* C, const void* r
   GemmParams p{M, N, K, ldc, C, reinterpret_cast<const __nv_bfloat16*>(residual), part_val, part_idx, part_lse, status, trace,
                nullptr, nullptr, 0, 1, 0, nullptr, nullptr, nullptr, nullptr, nullptr};
   p.m_fast = ((epi == EPI_ARGMAX || epi == EPI_TOPK) && M > BM) ? 1 : 0;
+  if (deep == 3) {     // two row tiles per CTA (256 x 256 output per CTA, 192 KB pipeline): many-row GEMMs
+    if (bn != 256 || split != 1) return -19;
+    if (epi == EPI_STORE) return launch_gemm<256, EPI_STORE, 192, false, 2>(ta, tw, p, 1, pdl != 0, stream);
+    if (epi == EPI_SWIGLU) return launch_gemm<256, EPI_SWIGLU, 192, false, 2>(ta, tw, p, 1, pdl != 0, stream);
+    return -19;
+  }
 #define JS_CASE(BN_, EPI_)                                                                              \
   if (bn == BN_ && epi == EPI_)                                                                         \
     return deep == 2 ? launch_gemm<BN_, EPI_, 128>(ta, tw, p, split, pdl != 0, stream)   \
