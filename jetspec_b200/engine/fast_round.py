@@ -926,6 +926,13 @@ class FastRound:
         fused GEMM+all-reduce).  Returns ``(first greedy token, tapped hidden (T, taps*H) or None)``."""
         pool, dev, cfg = self.eng.pool, self.device, self.cfg
         T, H = ids.shape[1], cfg.hidden_size
+        par = self.tp if self.tp is not None else self.ep
+        if par is not None:
+            # Graph capture and host-side set-up take a different time on every rank (seconds apart with eight
+            # processes sharing the host), while the kernels' waits on peers are bounded at about a second: line
+            # the ranks up on the host before the first exchange of the request.
+            import torch.distributed as dist
+            dist.barrier(group=par.group)
         pool.reserve(sid, total)
         row = pool.state(sid).row
         chunk = 512 if self.tp is None else min(512, self.tp.m_cap)

@@ -236,7 +236,14 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None)
     if bn is None and epi == EPI_STORE and m_tiles >= 4 and N % 256 == 0 and m_tiles * (N // 256) >= 64:
         # prefill / batched verify (>= 512 rows): compute bound, and a 128x128 tile asks more of the L2-to-SM path
         # than it gives; 128x256 tiles with the deep pipeline measured 5-12 % faster at 2048 rows
-        # (qkv 97 -> 91 us, o 62 -> 56, down 182 -> 165) and equal or better at 512
+        # (qkv 97 -> 91 us, o 62 -> 56, down 182 -> 165) and equal or better at 512.  From 1024 rows on, two row tiles
+        # per CTA (deep = 3: 256 x 256 outputs per CTA, every weight stage feeds two accumulators) when that does not
+        # cost a wave: at 2048 rows o 53.9 -> 48.7 us, down 155.4 -> 146.3 (128 CTAs, one wave), but qkv
+        # 88.1 -> 96.2 (192 CTAs: two waves of big tiles against three of small ones), gate/up equal.
+        if m_tiles >= 8:
+            t1, t2 = m_tiles * (N // 256), ((m_tiles + 1) // 2) * (N // 256)
+            if 2 * ((t2 + SM_COUNT - 1) // SM_COUNT) <= (t1 + SM_COUNT - 1) // SM_COUNT:
+                return 256, 1, 3
         return 256, 1, 1
     bn = bn or 128
     tiles = m_tiles * ((N + bn - 1) // bn)

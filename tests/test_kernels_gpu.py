@@ -63,6 +63,25 @@ def test_gemm_many_row_tiles_picks_wide_tiles(ext):
     ext.check_status("cuda")
 
 
+@pytest.mark.parametrize("M", [2048, 1000, 257, 129, 128])
+def test_gemm_two_row_tiles_per_cta(ext, M):
+    """deep = 3: one CTA computes two 128-row tiles (two accumulators) from every weight stage; row counts that leave
+    the second tile partly or wholly empty, store (+ residual) and SwiGLU epilogues."""
+    N, K = 1024, 768
+    x, w, r = rnd(M, K, seed=3), rnd(N, K, scale=0.05, seed=4), rnd(M, N, seed=5)
+    out = ext.gemm(x, w, residual=r, bn=256, split=1, deep=3)
+    torch.cuda.synchronize()
+    assert rel_err(out, x.float() @ w.float().t() + r.float()) < BF16_TOL
+    g, u = w[: N // 2], w[N // 2:]
+    act = ext.gemm(x, ext.interleave_gate_up(g, u, 256), epi=ext.EPI_SWIGLU, bn=256, split=1, deep=3)
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.silu(x.float() @ g.float().t()) * (x.float() @ u.float().t())
+    assert rel_err(act, ref) < BF16_TOL
+    ext.check_status("cuda")
+    assert ext.pick_gemm_config(2048, 4096, 4096, ext.EPI_STORE) == (256, 1, 3)     # 128 CTAs, one wave
+    assert ext.pick_gemm_config(2048, 6144, 4096, ext.EPI_STORE) == (256, 1, 1)     # would be two waves of big tiles
+
+
 def test_gemm_fp32_out(ext):
     x, w = rnd(64, 512, seed=6), rnd(128, 512, scale=0.05, seed=7)
     out = ext.gemm(x, w, epi=ext.EPI_STORE_F32, split=2)
