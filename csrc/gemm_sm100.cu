@@ -80,6 +80,11 @@ struct GemmParams {
   // (consecutive CTAs share the WEIGHT tile: for a vocabulary matrix larger than L2 and many row tiles, each
   // weight tile then comes from HBM once instead of once per row tile)
   int m_fast;
+  // Grouped mode: a row tile with at most this many rows left loads its activations through the second tensor map,
+  // whose box holds only that many rows (0 = always the 128-row box).  With ~8 rows per expert (MoE decode) a
+  // 128-row box would make the activations half of every stage's bytes although almost none of its rows are used;
+  // the accumulator rows beyond the box read stale shared memory and are never stored.
+  int a_small_rows;
 };
 
 JS_DEVICE void red_release_sys_add(int* addr, int v) {
@@ -138,7 +143,8 @@ __host__ __device__ inline bool recv_aliases_stages(int tiles_bytes, int recv_to
 
 template <int BN, int EPI, int BUDGET_KB, bool FP4 = false, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, GemmSmem<BN, BUDGET_KB, FP4, MT>::kMinBlocks)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                 const __grid_constant__ CUtensorMap tmA2, GemmParams p) {
   using S = GemmSmem<BN, BUDGET_KB, FP4, MT>;
   constexpr int kStages = S::kStages;
   static_assert(!FP4 || BN == 128, "the NVFP4 path is built for 128-column tiles");
@@ -196,6 +202,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     JS_TRACE(0);   // kernel start
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmW);
+    if (p.a_small_rows > 0) tma_prefetch_desc(&tmA2);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -234,21 +241,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           bulk_load_1d(smem + s * S::kStage + S::kStageA + S::kStageW,
                        p.sfa + static_cast<size_t>(m0 / 128) * sf_row + static_cast<size_t>(kb) * 2048, 2048, &full_bar[s]);
       };
+      // bytes a stage receives: the activation box shrinks for a row tile with few rows left (grouped mode)
+      auto small_tile = [&](int m_tile) { return p.a_small_rows > 0 && m_end - m_tile <= p.a_small_rows; };
+      auto stage_bytes = [&](bool small) {
+        return static_cast<uint32_t>(small ? S::kStage - S::kStageA + p.a_small_rows * BK * 2 : S::kStage);
+      };
+      const bool small0 = small_tile(m0);
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full_bar[i], S::kStage);
+        mbar_expect_tx(&full_bar[i], stage_bytes(small0));
         tma_load_2d(smem + i * S::kStage + S::kStageA, &tmW, &full_bar[i], (kb_begin + i) * kXStep, wn0);
         load_sfw(i, kb_begin + i);
       }
       pdl_wait();
       for (int i = 0; i < pre; ++i) {
+        if (small0) {
+          tma_load_2d(smem + i * S::kStage, &tmA2, &full_bar[i], (kb_begin + i) * kXStep, m0);
+        } else {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(smem + i * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0 + mt * BM);
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d(smem + i * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[i], (kb_begin + i) * kXStep, m0 + mt * BM);
+        }
         load_sfa(i, kb_begin + i);
       }
       bool p_ok = true;
       for (int tj = 0; tj < n_tiles_cta && p_ok; ++tj) {
         const int m_tile = m_first + tj * tile_step;
+        const bool small = small_tile(m_tile);
         for (int i = (tj == 0 ? pre : 0); i < nkb; ++i) {
           const int g = tj * nkb + i;              // running k-block count of this CTA
           const int s = g % kStages;
@@ -256,11 +274,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t ph = (g / kStages) & 1;
             if (!mbar_wait(&empty_bar[s], ph ^ 1, p.status, kTimeoutEmpty)) { p_ok = false; break; }
           }
-          mbar_expect_tx(&full_bar[s], S::kStage);
+          mbar_expect_tx(&full_bar[s], stage_bytes(small));
           tma_load_2d(smem + s * S::kStage + S::kStageA, &tmW, &full_bar[s], (kb_begin + i) * kXStep, wn0);
+          if (small) {
+            tma_load_2d(smem + s * S::kStage, &tmA2, &full_bar[s], (kb_begin + i) * kXStep, m_tile);
+          } else {
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            tma_load_2d(smem + s * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[s], (kb_begin + i) * kXStep, m_tile + mt * BM);
+            for (int mt = 0; mt < MT; ++mt)
+              tma_load_2d(smem + s * S::kStage + mt * (BM * BK * 2), &tmA, &full_bar[s], (kb_begin + i) * kXStep, m_tile + mt * BM);
+          }
           load_sfw(s, kb_begin + i);
           load_sfa(s, kb_begin + i);
         }
@@ -863,6 +885,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------- host side
+constexpr int kGroupedSmallRows = 32;     // rows of the small activation box of grouped launches (GemmParams::a_small_rows)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -909,7 +932,7 @@ static int make_map_u8(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t 
 
 template <int BN, int EPI, int BUDGET_KB, bool FP4 = false, int MT = 1>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmParams& p, int split, bool pdl,
-                       cudaStream_t stream, int groups = 0, int group_m_tiles = 0) {
+                       cudaStream_t stream, int groups = 0, int group_m_tiles = 0, const CUtensorMap* ta_small = nullptr) {
   using S = GemmSmem<BN, BUDGET_KB, FP4, MT>;
   static int configured[kMaxDevicesCached] = {};
   auto kern = gemm_bf16_kernel<BN, EPI, BUDGET_KB, FP4, MT>;
@@ -940,7 +963,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, const GemmP
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tw, p) == cudaSuccess ? 0 : -4;
+  if ((p.a_small_rows > 0) != (ta_small != nullptr)) return -19;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tw, ta_small ? *ta_small : ta, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace js
@@ -1036,18 +1060,21 @@ extern "C" int js_gemm_bf16_grouped(const void* A, const void* W, void* C, int t
   if (total_rows <= 0 || groups <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8) || (N % 128)) return -10;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
-  CUtensorMap ta, tw;
-  if (make_map(&ta, A, total_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128)) return -16;
+  CUtensorMap ta, tw, ta_small;
+  if (make_map(&ta, A, total_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128) ||
+      make_map(&ta_small, A, total_rows, K, lda, kGroupedSmallRows))
+    return -16;
   GemmParams p{total_rows, N, K, ldc, C, nullptr, nullptr, nullptr, nullptr, status, nullptr,
                nullptr, nullptr, 0, world, 0, group_off, row_pair, row_weight,
                reinterpret_cast<__nv_bfloat16* const*>(peer_pairs), peer_cnt};
+  p.a_small_rows = kGroupedSmallRows;
   const int m_tiles = (max_rows_per_group + BM - 1) / BM;
   if (m_tiles < 1) return 0;
-  if (epi == EPI_STORE) return launch_gemm<128, EPI_STORE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
-  if (epi == EPI_SWIGLU) return launch_gemm<128, EPI_SWIGLU, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+  if (epi == EPI_STORE) return launch_gemm<128, EPI_STORE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles, &ta_small);
+  if (epi == EPI_SWIGLU) return launch_gemm<128, EPI_SWIGLU, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles, &ta_small);
   if (epi == EPI_EP_COMBINE) {
     if (!row_pair || !row_weight || !peer_pairs || !peer_cnt) return -22;
-    return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+    return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles, &ta_small);
   }
   return -17;
 }
@@ -1064,16 +1091,19 @@ extern "C" int js_gemm_bf16_grouped_ep(const void* A, const void* W, int slab_ro
   if ((K % 8) || (lda % 8) || (ldw % 8) || (N % 128)) return -10;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
   if (!row_meta || !row_weight || !peer_pairs || world < 1) return -22;
-  CUtensorMap ta, tw;
-  if (make_map(&ta, A, slab_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128)) return -16;
+  CUtensorMap ta, tw, ta_small;
+  if (make_map(&ta, A, slab_rows, K, lda, BM) || make_map(&tw, W, static_cast<uint64_t>(groups) * N, K, ldw, 128) ||
+      make_map(&ta_small, A, slab_rows, K, lda, kGroupedSmallRows))
+    return -16;
   GemmParams p{};
+  p.a_small_rows = kGroupedSmallRows;
   p.M = slab_rows; p.N = N; p.K = K; p.ldc = N; p.status = status; p.world = world;
   p.group_off = group_off; p.row_weight = row_weight;
   p.peer_pairs = reinterpret_cast<__nv_bfloat16* const*>(peer_pairs);
   p.row_meta = reinterpret_cast<const int2*>(row_meta);
   const int m_tiles = (max_rows_per_group + BM - 1) / BM;
   if (m_tiles < 1) return 0;
-  return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles);
+  return launch_gemm<128, EPI_EP_COMBINE, 96>(ta, tw, p, 1, pdl != 0, stream, groups, m_tiles, &ta_small);
 }
 
 // NVFP4 GEMM: C[M,N] = (Aq * sfa * row_scale) * (Wq * sfw * w_scale)^T.  Aq (M, K/2) and Wq (N, K/2) hold two

@@ -926,18 +926,22 @@ class FastRound:
         fused GEMM+all-reduce).  Returns ``(first greedy token, tapped hidden (T, taps*H) or None)``."""
         pool, dev, cfg = self.eng.pool, self.device, self.cfg
         T, H = ids.shape[1], cfg.hidden_size
-        par = self.tp if self.tp is not None else self.ep
-        if par is not None:
-            # Graph capture and host-side set-up take a different time on every rank (seconds apart with eight
-            # processes sharing the host), while the kernels' waits on peers are bounded at about a second: line
-            # the ranks up on the host before the first exchange of the request.
-            import torch.distributed as dist
-            dist.barrier(group=par.group)
         pool.reserve(sid, total)
         row = pool.state(sid).row
         chunk = 512 if self.tp is None else min(512, self.tp.m_cap)
         if self.ep is not None:
             chunk = min(chunk, self.ep.max_tokens)
+        # Line the ranks up on the host before the first exchange of the request: graph capture and host-side set-up
+        # take a different time on every rank (seconds apart with eight processes sharing the host), while the
+        # kernels' waits on peers are bounded at about a second.  Under expert parallelism the same exchange tells
+        # every rank how many prompt chunks the longest prompt has: it must be known BEFORE the chunks run, because
+        # a rank with a shorter prompt has to keep serving the others' rows (`idle_layer`) right after its own.
+        chunks_all = None
+        if self.ep is not None:
+            chunks_all = self._all_max((T + chunk - 1) // chunk)
+        elif self.tp is not None:
+            import torch.distributed as dist
+            dist.barrier(group=self.tp.group)
         tap_ids = list(taps) if taps else None
         hidden = torch.empty(T, len(tap_ids) * H, dtype=torch.bfloat16, device=dev) if tap_ids else None
         seq_rows = torch.tensor([row], dtype=torch.int32, device=dev)
@@ -965,7 +969,7 @@ class FastRound:
             # every rank takes part in every expert-parallel layer call: ranks with shorter prompts sit the
             # remaining chunks out (their experts still serve the others' rows)
             mine = (T + chunk - 1) // chunk
-            for _ in range(self._all_max(mine) - mine):
+            for _ in range(chunks_all - mine):
                 for L in self.layers:
                     if L.get("moe_ep"):
                         gate_w, gu_l, dn_l, _, renorm = L["moe"]

@@ -111,7 +111,9 @@ def ep_engine_a3b_geometry(rank, world, dev) -> bool:
     model = Qwen3ForCausalLM.random_init(cfg, seed=4, dtype=torch.bfloat16, device="cuda", init="stable")
     head = DraftHeadModel.random_init(draft_head_config(cfg, num_layers=1, block_size=21, num_taps=3), seed=5,
                                       dtype=torch.bfloat16, device="cuda")
-    prompt = torch.randint(0, cfg.vocab_size, (1, 300 + 40 * rank), generator=torch.Generator().manual_seed(10 + rank))
+    # prompt lengths that need a different number of 128-token prefill chunks on every rank (2 on rank 0, 3 on rank 1,
+    # ... 6 on rank 7): the ranks with shorter prompts sit the others' extra chunks out and keep serving their rows
+    prompt = torch.randint(0, cfg.vocab_size, (1, 200 + 70 * rank), generator=torch.Generator().manual_seed(10 + rank))
     sp = SamplingParams(0.0, 96)
     want = [(int(prompt[0, -1]) + 1 + i) % cfg.vocab_size for i in range(96)]
     ep = TokenShardedEP(None, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, max_tokens=128)
