@@ -84,3 +84,24 @@ def test_llm_round_collector_runs_on_the_reference_engine_path():
             assert len(out["depth_rank_accept"]) == 4 and sum(out["meta"]["trials"]) > 0
         else:
             assert out["verdict"] in ("P3_BUILD", "P3_SKIP") and "lift" in out
+
+
+def test_kernel_config_pickers_on_cpu():
+    """Host-side launch policies that need no GPU: the GEMM picker's many-row rule and the attention split count."""
+    from jetspec_b200.ops import cuda_ext as X
+    # decode: one row tile, weight streaming -> K split over a cluster while the grid stays one wave
+    assert X.pick_gemm_config(128, 4096, 4096, X.EPI_STORE)[:2] == (128, 4)
+    assert X.pick_gemm_config(128, 6144, 4096, X.EPI_STORE)[:2] == (128, 2)
+    # many rows: 256-column tiles; two row tiles per CTA only where that does not add a wave of (bigger) tiles
+    assert X.pick_gemm_config(2048, 4096, 4096, X.EPI_STORE) == (256, 1, 3)
+    assert X.pick_gemm_config(2048, 4096, 12288, X.EPI_STORE) == (256, 1, 3)
+    assert X.pick_gemm_config(2048, 6144, 4096, X.EPI_STORE) == (256, 1, 1)
+    assert X.pick_gemm_config(512, 4096, 4096, X.EPI_STORE) == (256, 1, 1)
+    # attention: one wave of CTAs; 32 query tiles x heads leave 4 key splits, a shard with one KV head gets 16
+    assert X.attn_splits_for(128, 32, 8, 2700) == 4
+    assert X.attn_splits_for(128, 4, 1, 2700) == 16
+    assert X.attn_splits_for(2048, 32, 8, 2700) == 1
+    # in-cluster merge: up to 8 splits and only while every cluster of the launch is resident at once
+    assert X.attn_merges_in_cluster(128, 32, 8, 4)
+    assert not X.attn_merges_in_cluster(128, 32, 8, 16)
+    assert not X.attn_merges_in_cluster(128, 32, 8, 1)
