@@ -55,3 +55,16 @@ def test_tp_engine_four_ranks():
 def test_tp_engine_eight_ranks():
     rc, out = _launch(8, "engine", timeout=900)
     assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_expert_parallel_engine_four_ranks():
+    rc, out = _launch(4, "ep_engine")
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs 8 GPUs")
+def test_expert_parallel_engine_eight_ranks():
+    """Eight requests with prompts of 2 .. 6 prefill chunks and different round counts, 16 experts per rank."""
+    rc, out = _launch(8, "ep_engine", timeout=900)
+    assert rc == 0 and "TP_WORKER_OK" in out, out[-3000:]

@@ -117,7 +117,7 @@ def ep_engine_a3b_geometry(rank, world, dev) -> bool:
     sp = SamplingParams(0.0, 96)
     want = [(int(prompt[0, -1]) + 1 + i) % cfg.vocab_size for i in range(96)]
     ep = TokenShardedEP(None, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, max_tokens=128)
-    eng = JetSpecEngine(model, device=dev, dtype=torch.bfloat16, max_seq_len=1024, expert_parallel=ep)
+    eng = JetSpecEngine(model, device=dev, dtype=torch.bfloat16, max_seq_len=2048, expert_parallel=ep)
     ar = eng.generate(prompt, sp)["token_ids"]
     oracle = OracleTreeDrafter(prompt[0].tolist() + want, cfg.vocab_size, tree_width=7, mean_accept=3.0 + 2 * rank,
                                max_accept=19, seed=rank)
