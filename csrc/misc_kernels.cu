@@ -216,6 +216,52 @@ topk_merge_kernel(const float* part_val, const int* part_idx, const float* part_
   }
 }
 
+// First pass of a two-pass top-k over materialised fp32 logits (the few-rows vocabulary pass of a draft block: the
+// GEMM stores its logits with the plain fp32 epilogue, which streams the weights at the argmax epilogue's rate).
+// Block (slice, row) scans columns [slice * slice_cols, ...) of one row and emits that slice's sorted top-8 and
+// (max, sum of exp) in the layout of the GEMM's per-tile partials, so topk_merge_kernel finishes the row.
+__global__ void __launch_bounds__(256)
+logits_topk_slice_kernel(const float* logits, long long ld, int N, int M, int slice_cols, float* part_val, int* part_idx,
+                         float* part_lse) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.y, sl = blockIdx.x, n_slices = gridDim.x;
+  if (row >= M) return;
+  __shared__ float win_v[8];
+  __shared__ int win_i[8];
+  __shared__ float row_m, row_s;
+  const int c0 = sl * slice_cols, c1 = min(N, c0 + slice_cols);
+  float lv[8];
+  int li[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { lv[e] = -INFINITY; li[e] = 0x7fffffff; }
+  float mx = -INFINITY, se = 0.f;
+  const float* src = logits + static_cast<size_t>(row) * ld;
+  for (int c = c0 + 4 * static_cast<int>(threadIdx.x); c < c1; c += 4 * 256) {     // N, slice_cols, ld: multiples of 4
+    const float4 q = *reinterpret_cast<const float4*>(src + c);
+    const float v[4] = {q.x, q.y, q.z, q.w};
+    const float cm = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+    if (cm != -INFINITY) {
+      const float nm = fmaxf(mx, cm);
+      se = (mx == -INFINITY ? 0.f : se * __expf(mx - nm)) + __expf(v[0] - nm) + __expf(v[1] - nm) + __expf(v[2] - nm) +
+           __expf(v[3] - nm);
+      mx = nm;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) topk_insert(lv, li, v[j], c + j);
+  }
+  topk_block_finish(lv, li, mx, se, 8, win_v, win_i, &row_m, &row_s);
+  const size_t o = static_cast<size_t>(row) * n_slices + sl;
+  if (threadIdx.x < 8) {
+    part_val[o * 8 + threadIdx.x] = win_v[threadIdx.x];
+    part_idx[o * 8 + threadIdx.x] = win_i[threadIdx.x];
+  }
+  if (threadIdx.x == 0) {
+    part_lse[o * 2] = row_m;
+    part_lse[o * 2 + 1] = row_s;
+  }
+}
+
 static cudaLaunchAttribute g_pdl_attr;
 static void launch_cfg(cudaLaunchConfig_t& c, dim3 grid, dim3 block, cudaStream_t stream, int pdl) {
   c = cudaLaunchConfig_t{};
@@ -283,6 +329,17 @@ extern "C" int js_argmax_merge(const float* part_val, const int* part_idx, int n
                                float* out_val, int pdl, cudaStream_t stream) {
   if (M <= 0) return 0;
   JS_LAUNCH(js::argmax_merge_kernel, dim3((M + 7) / 8), dim3(256), part_val, part_idx, n_tiles, M, out_idx, out_val);
+}
+
+// Slice partials of materialised logits (M, N) fp32 with leading dimension ld: part_val / part_idx (M, n_slices, 8),
+// part_lse (M, n_slices, 2); finish with js_topk_merge(..., n_tiles = n_slices, ...).
+extern "C" int js_logits_topk_slices(const float* logits, long long ld, int M, int N, int n_slices, float* part_val,
+                                     int* part_idx, float* part_lse, int pdl, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (n_slices < 1 || (N % 4) || (ld % 4) || (reinterpret_cast<uintptr_t>(logits) & 15)) return -10;
+  const int slice_cols = (((N + n_slices - 1) / n_slices) + 3) / 4 * 4;
+  JS_LAUNCH(js::logits_topk_slice_kernel, dim3(n_slices, M), dim3(256), logits, ld, N, M, slice_cols, part_val, part_idx,
+            part_lse);
 }
 
 extern "C" int js_topk_merge(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles, int M,

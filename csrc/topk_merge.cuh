@@ -11,6 +11,23 @@ namespace js {
 // larger value first; among equal values the lower token id
 JS_DEVICE bool cand_better(float v1, int i1, float v2, int i2) { return v1 > v2 || (v1 == v2 && i1 < i2); }
 
+JS_DEVICE void topk_block_finish(float (&lv)[8], int (&li)[8], float mx, float se, int K, float* win_v, int* win_i,
+                                 float* row_m, float* row_s);
+
+// sorted insertion of one candidate into a private top-8 (larger value first, lower id first among equals)
+JS_DEVICE void topk_insert(float (&lv)[8], int (&li)[8], float v, int ix) {
+  if (!cand_better(v, ix, lv[7], li[7])) return;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    if (cand_better(v, ix, lv[q], li[q])) {
+      const float fv = lv[q];
+      const int fi = li[q];
+      lv[q] = v; li[q] = ix;
+      v = fv; ix = fi;
+    }
+  }
+}
+
 // Called by all 256 threads of a block for one row.  Each thread folds the sorted 8-entry lists of its tiles
 // into a private sorted top-8 (registers, one pass over global memory, coalesced 32-byte reads), then K
 // block-wide argmax rounds over the threads' list heads pick the row's top-K.  Vocabulary tiles are disjoint,
@@ -19,11 +36,7 @@ JS_DEVICE bool cand_better(float v1, int i1, float v2, int i2) { return v1 > v2 
 // valid for every thread after the function returns (it ends with a block barrier).
 JS_DEVICE void topk_merge_row(const float* part_val, const int* part_idx, const float* part_lse, int n_tiles, int row,
                               int K, float* win_v, int* win_i, float* row_m, float* row_s) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  constexpr int kWarps = 8;
-  __shared__ float s_m[kWarps], s_s[kWarps];
-  __shared__ float s_v[2][kWarps];
-  __shared__ int s_i[2][kWarps];
+  const int tid = threadIdx.x;
   float lv[8];
   int li[8];
 #pragma unroll
@@ -58,6 +71,19 @@ JS_DEVICE void topk_merge_row(const float* part_val, const int* part_idx, const 
       }
     }
   }
+  topk_block_finish(lv, li, mx, se, K, win_v, win_i, row_m, row_s);
+}
+
+// Second half of the row merge, shared with the kernel that scans raw logits: every thread of the 256-thread block
+// brings a private sorted top-8 (lv, li) and a running (max, sum of exp); the block's (max, sum) goes to *row_m,
+// *row_s and K block-wide argmax rounds over the threads' list heads fill win_v / win_i.  Ends with a block barrier.
+JS_DEVICE void topk_block_finish(float (&lv)[8], int (&li)[8], float mx, float se, int K, float* win_v, int* win_i,
+                                 float* row_m, float* row_s) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = 8;
+  __shared__ float s_m[kWarps], s_s[kWarps];
+  __shared__ float s_v[2][kWarps];
+  __shared__ int s_i[2][kWarps];
   // log-sum-exp of the row: warp shuffle, then the 8 warp results
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

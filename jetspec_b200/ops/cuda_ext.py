@@ -404,6 +404,13 @@ def lm_head_argmax(h: torch.Tensor, w: torch.Tensor, ws: Optional[dict] = None, 
     return out_idx, out_val
 
 
+# Few-row top-k over the vocabulary in two passes over materialised logits (JETSPEC_TOPK_TWO_PASS=0: inside the GEMM
+# epilogue, as for many rows).  The partial lists reuse the epilogue's workspace: (rows, slices, 8) fits (rows, tiles, 8).
+TOPK_TWO_PASS = os.environ.get("JETSPEC_TOPK_TWO_PASS", "1") != "0"
+TOPK_TWO_PASS_ROWS = 32
+TOPK_SLICES = 64
+
+
 def lm_head_topk_logprobs(h: torch.Tensor, w: torch.Tensor, k: int, ws: Optional[dict] = None, pdl: bool = False,
                           out_tok: Optional[torch.Tensor] = None, out_lp: Optional[torch.Tensor] = None):
     """Per-row top-``k`` tokens with full-vocabulary log-probabilities, without materialising logits."""
@@ -415,12 +422,27 @@ def lm_head_topk_logprobs(h: torch.Tensor, w: torch.Tensor, k: int, ws: Optional
         ws = {"val": torch.empty(M, nt, 8, dtype=torch.float32, device=h.device),
               "idx": torch.empty(M, nt, 8, dtype=torch.int32, device=h.device),
               "lse": torch.empty(M, nt, 2, dtype=torch.float32, device=h.device)}
-    gemm(h, w, out=None, epi=EPI_TOPK, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"],
-         part_lse=ws["lse"])
     if out_tok is None:
         out_tok = torch.empty(M, k, dtype=torch.int32, device=h.device)
     if out_lp is None:
         out_lp = torch.empty(M, k, dtype=torch.float32, device=h.device)
+    if TOPK_TWO_PASS and M <= TOPK_TWO_PASS_ROWS and N % 4 == 0 and nt >= TOPK_SLICES:
+        # A draft block has a few rows, so one warp per CTA would carry the in-epilogue sorted insertion and the
+        # weight stream stalls behind it.  Store the (few) logits with the plain fp32 epilogue instead, which streams
+        # at the argmax epilogue's rate, and take the top-k from them in two small passes (they stay in L2).
+        if "logits" not in ws or ws["logits"].shape[0] < M or ws["logits"].shape[1] != N:
+            ws["logits"] = torch.empty(max(M, TOPK_TWO_PASS_ROWS), N, dtype=torch.float32, device=h.device)
+        logits = ws["logits"][:M]
+        gemm(h, w, out=logits, epi=EPI_STORE_F32, bn=128, split=1, pdl=pdl)
+        lib.js_logits_topk_slices.restype = ctypes.c_int
+        _check(lib.js_logits_topk_slices(_p(logits), ctypes.c_longlong(logits.stride(0)), M, N, TOPK_SLICES,
+                                         _p(ws["val"]), _p(ws["idx"]), _p(ws["lse"]), int(pdl), _stream()),
+               "js_logits_topk_slices")
+        _check(lib.js_topk_merge(_p(ws["val"]), _p(ws["idx"]), _p(ws["lse"]), TOPK_SLICES, M, k, _p(out_tok),
+                                 _p(out_lp), int(pdl), _stream()), "js_topk_merge")
+        return out_tok, out_lp
+    gemm(h, w, out=None, epi=EPI_TOPK, bn=128, split=1, pdl=pdl, part_val=ws["val"], part_idx=ws["idx"],
+         part_lse=ws["lse"])
     _check(lib.js_topk_merge(_p(ws["val"]), _p(ws["idx"]), _p(ws["lse"]), nt, M, k, _p(out_tok), _p(out_lp),
                              int(pdl), _stream()), "js_topk_merge")
     return out_tok, out_lp

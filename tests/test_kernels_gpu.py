@@ -140,6 +140,25 @@ def test_lm_head_topk_logprobs(ext, M):
     assert torch.allclose(lp, ref_lp_all.gather(1, tok.long()), atol=2e-3, rtol=0)
 
 
+@pytest.mark.parametrize("M", [1, 21, 32])
+def test_lm_head_topk_two_pass_matches_epilogue(ext, M, monkeypatch):
+    """Few rows over a vocabulary of many tiles: logits stored by the fp32 epilogue + slice pass + merge against the
+    in-epilogue top-k and against the fp32 reference (a vocabulary that is not a multiple of the slice width)."""
+    V, H, K = 20004, 512, 8
+    h, w = rnd(M, H, seed=13), rnd(V, H, scale=0.08, seed=14)
+    assert ext.TOPK_TWO_PASS and M <= ext.TOPK_TWO_PASS_ROWS and ext.n_tiles(V) >= ext.TOPK_SLICES
+    tok2, lp2 = ext.lm_head_topk_logprobs(h, w, K)
+    monkeypatch.setattr(ext, "TOPK_TWO_PASS", False)
+    tok1, lp1 = ext.lm_head_topk_logprobs(h, w, K)
+    torch.cuda.synchronize()
+    assert torch.equal(tok1, tok2)                       # same fp32 accumulators, same order and tie-break
+    assert torch.allclose(lp1, lp2, atol=1e-5, rtol=0)
+    ref_lp_all = torch.log_softmax(h.float() @ w.float().t(), -1)
+    assert torch.allclose(lp2, ref_lp_all.gather(1, tok2.long()), atol=2e-3, rtol=0)
+    assert torch.allclose(lp2, torch.topk(ref_lp_all, K, -1).values, atol=2e-3, rtol=0)
+    ext.check_status("cuda")
+
+
 def test_elementwise(ext):
     from jetspec_b200.ops import reference as ref
     x, w = rnd(37, 4096, seed=15), rnd(4096, seed=16)
