@@ -1,6 +1,7 @@
 """Small stand-alone kernel cases for profiling (one kernel family per case, a few launches).
 
     python bench/kernel_cases.py gemm        # the four decoder GEMM shapes of Qwen3-8B at 128 rows
+    python bench/kernel_cases.py gemm_rows2048   # the same shapes at 2048 rows (batched verify / prefill tiles)
     python bench/kernel_cases.py attention   # paged tree attention, 128 nodes over a 1.5k-token prefix
     python bench/kernel_cases.py lm_head     # vocabulary GEMM with the argmax epilogue
     python bench/kernel_cases.py nvfp4       # activation quantiser + block-scaled GEMM on the same four shapes
@@ -35,6 +36,24 @@ def case_gemm(reps: int = 2):
         X.gemm(x, w["qkv"])
         X.gemm(x, w["o"], out=res, residual=res)
         X.gemm(x, w["gu"], epi=X.EPI_SWIGLU)
+        X.gemm(a, w["down"], out=res, residual=res)
+    torch.cuda.synchronize()
+
+
+def case_gemm_rows2048(reps: int = 2):
+    """The same four shapes at 2048 rows (16 requests x 128 tree nodes, or a prefill chunk), picked configurations:
+    256-column tiles, two row tiles per CTA for o_proj / down_proj, 256-interleaved gate/up."""
+    M, H, I = 2048, 4096, 12288
+    x, a = bf(M, H), bf(M, I)
+    g, u = bf(I, H, scale=0.02), bf(I, H, scale=0.02)
+    w = {"qkv": bf(6144, H, scale=0.02), "o": bf(H, H, scale=0.02), "gu": X.interleave_gate_up(g, u, 256),
+         "down": bf(H, I, scale=0.02)}
+    del g, u
+    res = bf(M, H)
+    for _ in range(reps):
+        X.gemm(x, w["qkv"])
+        X.gemm(x, w["o"], out=res, residual=res)
+        X.gemm(x, w["gu"], epi=X.EPI_SWIGLU, bn=256, split=1, deep=0)
         X.gemm(a, w["down"], out=res, residual=res)
     torch.cuda.synchronize()
 
@@ -166,7 +185,7 @@ def case_collectives(reps: int = 3):
 
 if __name__ == "__main__":
     X.load()
-    {"gemm": case_gemm, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4,
+    {"gemm": case_gemm, "gemm_rows2048": case_gemm_rows2048, "lm_head": case_lm_head, "attention": case_attention, "nvfp4": case_nvfp4,
      "round_small": case_round_small, "collectives": case_collectives}[sys.argv[1]]()
     X.check_status("cuda")
     print("ok")
