@@ -127,8 +127,10 @@ def main():
         "prompt_lens": f"uniform [{args.prompt_lo}, {args.prompt_hi}]", "new_tokens": args.new,
         "tree": f"depth {args.tree_depth} width {args.tree_width} budget {args.budget}",
         "drafter": "oracle script per request (no draft-head forward in this bench)",
-        "ar_tokens_per_s": round(ar_tokens / ar_s, 1), "tree_tokens_per_s": round(toks / tree_s, 1),
-        "speedup": round((toks / tree_s) / (ar_tokens / ar_s), 3), "tokens_per_round": round(acc / max(1, rounds), 3),
+        "ar_tokens_per_s": None if args.skip_ar else round(ar_tokens / ar_s, 1),
+        "tree_tokens_per_s": round(toks / tree_s, 1),
+        "speedup": None if args.skip_ar else round((toks / tree_s) / (ar_tokens / ar_s), 3),
+        "tokens_per_round": round(acc / max(1, rounds), 3),
         "batch_rounds": max(o["rounds"] for o in out), "ms_per_batch_round": round(tree_s * 1e3 / max(o["rounds"] for o in out), 2),
         "tokens_per_s_per_request": round(toks / tree_s / args.batch, 1),
         "oracle_converged": converged, "timing": "wall clock around the public call, prefill included"}))
