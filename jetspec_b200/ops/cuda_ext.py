@@ -201,7 +201,8 @@ def inv_freq(head_dim: int, theta: float, device) -> torch.Tensor:
 EPI_STORE, EPI_SWIGLU, EPI_ARGMAX, EPI_TOPK, EPI_STORE_F32 = 0, 1, 2, 3, 4
 SM_COUNT = 148
 _DEEP = os.environ.get("JETSPEC_GEMM_DEEP", "0") == "1"
-_SPLIT_DEEP = int(os.environ.get("JETSPEC_SPLIT_DEEP", "1"))
+_SPLIT_DEEP = os.environ.get("JETSPEC_SPLIT_DEEP")      # force the split-K pipeline: 1 = 192 KB, 2 = 128 KB, 0 = 96 KB
+_SPLIT_DEEP = int(_SPLIT_DEEP) if _SPLIT_DEEP is not None else None
 
 
 # measured best (bn, split, deep) per (M, N, K, epilogue); filled from the tuning sweep
@@ -262,10 +263,15 @@ def pick_gemm_config(M: int, N: int, K: int, epi: int, bn: Optional[int] = None)
                 split = c
                 break
     if split > 1:
-        # deep pipeline (192 KB, one CTA per SM; the receive area aliases the stages) unless JETSPEC_SPLIT_DEEP picks
-        # 2 (128 KB) or 0 (96 KB: two kernels' CTAs can share an SM, so the next kernel's prologue and first weight
-        # stages overlap this one's epilogue)
-        return bn, split, _SPLIT_DEEP
+        # deep pipeline (192 KB, one CTA per SM; the receive area aliases the stages), except for the narrow shards of
+        # a tensor-parallel rank (at most 96 CTAs with at most 16 k-blocks each): 128 KB serves those as well and
+        # leaves room for the next kernel's CTA and its first weight stages on the same SM (compute-only round of a
+        # 1/8 shard: 2.96 -> 2.92 ms).  The full-size o_proj (128 CTAs) measured slower that way inside the round
+        # (5.45 -> 5.50 ms) although faster in a chain of its own.  JETSPEC_SPLIT_DEEP forces 1 (192 KB), 2 (128 KB)
+        # or 0 (96 KB) for every split launch.
+        if _SPLIT_DEEP is not None:
+            return bn, split, _SPLIT_DEEP
+        return bn, split, (2 if (kb + split - 1) // split <= 16 and tiles * split <= 96 else 1)
     # no split: a deep pipeline when the tiles fit one CTA per SM, else two shallow CTAs per SM
     return bn, 1, (1 if tiles <= SM_COUNT or _DEEP else 0)
 
