@@ -143,10 +143,13 @@ __global__ void moe_invert_kernel(const int* __restrict__ order, int P, int* __r
 }
 
 // out[t] = sum_j row_weight[r] * ys[r], r = inv[t*k + j], summed in choice order j = 0..k-1 in fp32
-// (no atomics: a token's result does not depend on how the other tokens were routed or scheduled)
+// (no atomics: a token's result does not depend on how the other tokens were routed or scheduled).
+// With `residual` (same shape and leading dimension as out, may be out itself) the result is
+// residual + bf16(sum): the rounding of a separate bf16 add after the combine, without its launch.
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, int ld, const int* __restrict__ inv,
-                   const float* __restrict__ row_weight, int T, int k, int H, __nv_bfloat16* __restrict__ out, int ldo) {
+                   const float* __restrict__ row_weight, int T, int k, int H, const __nv_bfloat16* residual,
+                   __nv_bfloat16* out, int ldo) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -171,6 +174,15 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, int ld, const int* __re
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    if (residual != nullptr) {
+      const uint4 rr = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * ldo + c);
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(o2[e]), b = __bfloat1622float2(r2[e]);
+        o2[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+      }
+    }
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ldo + c) = o;
   }
 }
@@ -221,8 +233,9 @@ extern "C" int js_moe_sort(const int* idx, const float* wts, int P, int E, int f
 
 // ys (T*k, H) bf16 in expert-sorted row order -> out (T, H) bf16: each token's k expert outputs weighted and
 // summed in choice order.  `inv` is a (T*k) int32 scratch.  H a multiple of 8, rows 16-byte aligned.
+// residual (optional, (T, H) with leading dimension ldo, may be `out`): out = residual + bf16(sum).
 extern "C" int js_moe_combine(const void* ys, int ld, const int* order, const float* row_weight, int T, int k, int H,
-                              int* inv, void* out, int ldo, int pdl, cudaStream_t stream) {
+                              int* inv, const void* residual, void* out, int ldo, int pdl, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (k < 1 || H % 8 || ld % 8 || ldo % 8) return -10;
   const int P = T * k;
@@ -239,6 +252,6 @@ extern "C" int js_moe_combine(const void* ys, int ld, const int* order, const fl
   c.gridDim = dim3(T);
   c.blockDim = dim3(128);
   return cudaLaunchKernelEx(&c, js::moe_combine_kernel, static_cast<const __nv_bfloat16*>(ys), ld,
-                            static_cast<const int*>(inv), row_weight, T, k, H, static_cast<__nv_bfloat16*>(out),
-                            ldo) == cudaSuccess ? 0 : -4;
+                            static_cast<const int*>(inv), row_weight, T, k, H,
+                            static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), ldo) == cudaSuccess ? 0 : -4;
 }

@@ -267,8 +267,8 @@ def decoder_layers(cfg, layers, st: _Stack, k_pools, v_pools, slot_map, seq_rows
             continue
         if "moe" in L:
             gate_w, w_gu, w_dn, top_k, renorm = L["moe"]
-            st.x.add_(X.moe_forward(st.h, gate_w, w_gu, w_dn, top_k, renorm))
-            n += 5 + merge_launch + 7          # + router GEMM, route, sort, two grouped GEMMs, invert and combine
+            X.moe_forward(st.h, gate_w, w_gu, w_dn, top_k, renorm, residual=st.x)     # st.x += MoE(st.h), in the combine kernel
+            n += 5 + merge_launch + 8          # + router GEMM, route, sort, row gather, two grouped GEMMs, invert, combine (+ residual)
             if taps is not None and li != last:
                 for j, t in enumerate(tap_ids):
                     if t == li:

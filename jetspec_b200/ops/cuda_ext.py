@@ -685,9 +685,10 @@ def kv_compact(k: torch.Tensor, v: torch.Tensor, past_len: int, keep: torch.Tens
 _moe_cache: dict = {}
 
 
-def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_logits=None):
+def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_logits=None, residual=None):
     """Sparse MoE on one GPU: route, sort the (token, choice) pairs by expert, run all experts'
-    SwiGLU MLPs with two grouped tcgen05 GEMMs (one launch each), combine with the routing weights."""
+    SwiGLU MLPs with two grouped tcgen05 GEMMs (one launch each), combine with the routing weights.
+    With ``residual`` (T, H) the combine kernel adds the layer output onto it in place and returns it."""
     from . import reference as ref
     from ..parallel.ep import interleave_experts, route_and_sort
     lib = load()
@@ -695,7 +696,8 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
     E, I2, _ = w_gate_up.shape
     I = I2 // 2
     if I % 64 or H % 128:
-        return ref.moe_forward(x, gate_w, w_gate_up, w_down, top_k, renorm, router_logits)
+        y = ref.moe_forward(x, gate_w, w_gate_up, w_down, top_k, renorm, router_logits)
+        return y if residual is None else residual.add_(y)
     key = (w_gate_up.data_ptr(), w_down.data_ptr())
     if key not in _moe_cache:
         _moe_cache[key] = (interleave_experts(w_gate_up), w_down.reshape(E * H, I).contiguous())
@@ -708,7 +710,11 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
     else:
         order, row_w, group_off, _ = route_and_sort(router_logits, top_k, renorm, 0, E)
         tok = torch.div(order, top_k, rounding_mode="floor")
-    xs = x.index_select(0, tok)
+    if on_device and x.dtype == torch.bfloat16 and x.stride(1) == 1:
+        xs = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
+        gather_rows(x, tok, xs)                   # expert-sorted copy of the token rows
+    else:
+        xs = x.index_select(0, tok)
     h = torch.empty(T * top_k, I, dtype=x.dtype, device=x.device)
     ys = torch.empty(T * top_k, H, dtype=x.dtype, device=x.device)
     st = _p(status_word(x.device))
@@ -723,12 +729,15 @@ def moe_forward(x, gate_w, w_gate_up, w_down, top_k: int, renorm: bool, router_l
            "grouped down")
     if on_device and x.dtype == torch.bfloat16:
         # weighted sum of each token's expert outputs in choice order (fixed order, no atomics)
-        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        fused = residual is not None and residual.dtype == x.dtype and residual.stride(1) == 1
+        out = residual if fused else torch.empty(T, H, dtype=x.dtype, device=x.device)
         inv = torch.empty(T * top_k, dtype=torch.int32, device=x.device)
         lib.js_moe_combine.restype = ctypes.c_int
-        _check(lib.js_moe_combine(_p(ys), ys.stride(0), _p(order), _p(row_w), T, top_k, H, _p(inv), _p(out),
-                                  out.stride(0), 0, _stream()), "js_moe_combine")
-        return out
+        _check(lib.js_moe_combine(_p(ys), ys.stride(0), _p(order), _p(row_w), T, top_k, H, _p(inv),
+                                  _p(residual) if fused else None, _p(out), out.stride(0), 0, _stream()),
+               "js_moe_combine")
+        return out if fused or residual is None else residual.add_(out)
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
     out.index_add_(0, tok.long(), ys.float() * row_w[:, None])
-    return out.to(x.dtype)
+    out = out.to(x.dtype)
+    return out if residual is None else residual.add_(out)

@@ -321,6 +321,12 @@ def test_grouped_moe_matches_reference(ext, T):
     exp = ref.moe_forward(x.float(), gate.float(), wgu.float(), wd.float(), k, True, router_logits=logits)
     torch.cuda.synchronize()
     assert rel_err(out, exp) < 2 * BF16_TOL
+    # residual fused into the combine kernel: exactly the rounding of a separate bf16 add
+    res = rnd(T, H, seed=34)
+    want = res + out
+    got = ext.moe_forward(x, gate, wgu, wd, k, True, router_logits=logits, residual=res)
+    torch.cuda.synchronize()
+    assert got.data_ptr() == res.data_ptr() and torch.equal(got, want)
     ext.check_status("cuda")
 
 
