@@ -1,7 +1,7 @@
 """Raw autoregressive decode baseline: prefill, then one-token steps, decode-only timing.
 
 The denominator of every "speedup over autoregressive decoding" figure, measured on its own (counterpart of the
-reference's ``bench/reference/hf_fa2_decode_baseline.py``, which times a stock Hugging Face model with
+reference's ``bench/reference/hf_fa2_decode_baseline.py:52-199``, which times a stock Hugging Face model with
 FlashAttention-2).  Three arms on the same prompt, each reporting prefill time, decode time and decode tokens/s:
 
 * ``engine``: this framework's paged engine; on a GPU every step is one CUDA-graph replay of the kernel path

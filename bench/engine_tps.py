@@ -1,6 +1,7 @@
 """Wall-clock throughput of the paged engine: AR vs tree-speculative, with data-parallel prompt sharding.
 
-Counterpart of the reference's ``bench/engine/tps_walltime.py``: every rank (``torchrun``) holds a full
+Counterpart of the reference's ``bench/engine/tps_walltime.py:164-306`` (rank sharding ``:85-139``, drafter
+construction ``:142-161``): every rank (``torchrun``) holds a full
 model replica and takes ``bank[rank::world]``; throughput is total tokens over the slowest rank's wall
 time, reduced with NCCL (gloo on CPU).  Prompts are synthetic token sequences (no dataset or tokenizer
 is needed); ``--prompt-set`` picks a length profile named after the reference's eight prompt sets.

@@ -1,6 +1,8 @@
 """Paged engine: AR vs batched decode, checking that a batch reproduces per-prompt outputs.
 
-    python examples/engine_generate.py [/path/to/model]"""
+    python examples/engine_generate.py [/path/to/model]
+
+Reference counterpart: ``examples/engine/jetspec_engine_generate.py:19-64``."""
 import os
 import sys
 

@@ -2,7 +2,8 @@
 
     python examples/simple_generate.py /path/to/Qwen3-8B "The capital of France is"
 
-Without arguments a tiny random-init model is used so the script runs anywhere (CPU included)."""
+Without arguments a tiny random-init model is used so the script runs anywhere (CPU included).
+Reference counterpart: ``examples/basic/simple_generate.py:10-21``."""
 import os
 import sys
 

@@ -1,7 +1,8 @@
 """Sweep tree algorithms x budgets and report tokens per verify forward and the exact-prefix length
 against plain greedy decoding (bf16 may flip a near-tie after many exact tokens; fp32 is exact).
 
-Environment: JETSPEC_SWEEP_BUDGETS="8,16,32", JETSPEC_SWEEP_WIDTH=4, JETSPEC_SWEEP_MAXNEW=48."""
+Environment: JETSPEC_SWEEP_BUDGETS="8,16,32", JETSPEC_SWEEP_WIDTH=4, JETSPEC_SWEEP_MAXNEW=48.
+Reference counterpart: ``examples/tree/jetspec_tree_algo_sweep.py:55-120`` (exact-prefix report ``:69-74``)."""
 import os
 import sys
 

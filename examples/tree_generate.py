@@ -2,7 +2,8 @@
 
     python examples/tree_generate.py /path/to/Qwen3-8B /path/to/draft-head "prompt"
 
-Without arguments: tiny random target + random head on CPU (lossless, low acceptance)."""
+Without arguments: tiny random target + random head on CPU (lossless, low acceptance).
+Reference counterpart: ``examples/tree/jetspec_tree_generate.py:25-51``."""
 import os
 import sys
 

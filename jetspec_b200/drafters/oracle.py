@@ -13,7 +13,8 @@ a confident trained head.
 The draw depends only on ``(seed, context length)``, so two engines handed the
 same drafter see the same trees and the same acceptance sequence.  The drafter
 speaks both contracts: dense ``propose_logits`` ``(1, D, V)`` and the direct
-``propose_topk`` ``(D, K)``.
+``propose_topk`` ``(D, K)`` (the ``TreeDrafter`` contract of ``jetspec/draft.py:36-161``, whose stub drafters play
+the same role for plumbing tests: full-accept ``TargetEchoTreeDrafter``, low-accept ``RandomTreeDrafter``).
 """
 from __future__ import annotations
 

@@ -10,7 +10,9 @@ Drafter process::
 
     DraftWorker(head, embed_weight, lm_head_weight, chan, width=K).serve()    # one request
 
-Both replay CUDA graphs; see :mod:`jetspec_b200.parallel.handoff` for the protocol.
+Both replay CUDA graphs; see :mod:`jetspec_b200.parallel.handoff` for the protocol.  The reference keeps the head on
+the target's device because it borrows the target's embedding and LM-head modules
+(``jetspec/draft_head_adapter.py:54,73,129``); here the drafter process holds its own copies of the two matrices.
 """
 from __future__ import annotations
 

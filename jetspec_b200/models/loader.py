@@ -4,6 +4,10 @@ Loads straight into the parameters of an already-constructed module, one tensor
 at a time, so a 16 GB checkpoint never exists twice in host memory.  A ``remap``
 callable can redirect a checkpoint key to ``(parameter_name, index)`` so that
 per-expert MoE tensors land inside the stacked expert parameters.
+
+The reference loads its target through Hugging Face ``from_pretrained`` (``jetspec/models/qwen3.py:38-71``) and
+fuses experts afterwards (``jetspec/models/moe_fused.py:16-116``); here the same checkpoint files are read directly
+into this framework's own modules, whose parameter names are the stock ones.
 """
 from __future__ import annotations
 

@@ -3,7 +3,8 @@
 Routing rule: a CUDA bf16 tensor goes to the hand-written kernel in the compiled
 extension (and raises if the extension is not loadable — no silent fallback on a
 GPU); CPU tensors, and non-bf16 CUDA tensors used by oracle tests, go to the plain
-PyTorch implementation in :mod:`jetspec_b200.ops.reference`.
+PyTorch implementation in :mod:`jetspec_b200.ops.reference`.  The reference's own seam of this kind is its
+``torch.library`` op around the Triton kernel (``jetspec/inference_engine/paged_tree_attn_op.py:29-79``).
 """
 from __future__ import annotations
 

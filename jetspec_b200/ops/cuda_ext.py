@@ -10,6 +10,12 @@ graph-capturable).
 
 On a machine with a GPU a missing or unloadable library is an error, never a
 silent fallback.
+
+What these kernels stand in for in the reference: the fused verify stack's cuBLAS GEMMs and ATen glue
+(``jetspec/inference_engine/compiled_verify_stack.py:170-272``), the Triton paged tree-attention kernel
+(``jetspec/inference_engine/paged_tree_attn.py:55-367``, op wrapper ``paged_tree_attn_op.py:29-79``), the dense
+tree-attention kernel of the HF path (``jetspec/core/tree_attention_kernel.py:63-216``), the graphed accept
+(``jetspec/inference_engine/graph_capture.py:240-323``) and the grouped-GEMM MoE (``jetspec/models/moe_fused.py:16-116``).
 """
 from __future__ import annotations
 

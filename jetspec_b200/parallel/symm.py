@@ -4,7 +4,8 @@ Each rank allocates the same-sized buffer with the kernel library's allocator, t
 IPC handles travel through the host process group, and every rank maps all peers'
 buffers.  ``ptrs_dev`` is a device array of ``world`` addresses (this rank's own buffer at
 index ``rank``) that the fused compute+collective kernels index by rank; they reach peer
-memory with plain loads and stores over NVLink.
+memory with plain loads and stores over NVLink.  (No counterpart in the reference, whose only collectives are the
+benchmark's NCCL reductions, ``bench/engine/tps_walltime.py:111-139``.)
 """
 from __future__ import annotations
 

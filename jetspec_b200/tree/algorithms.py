@@ -13,10 +13,13 @@ shared best-first builder.  They differ only in how the caps are chosen:
 ``class_histogram``    class template, or per-class offline histogram if given
 =====================  =========================================================
 
-Each recovers ``accum_logp`` bit-for-bit at its identity knob.  References:
-``jetspec/tree/baselines/accum_logp.py``, ``…/fanout_cap/top2gap.py``,
-``…/profile_guided/depth_rank_histogram.py``, ``…/semantic_aware/{task_router,
-reasoning_router,class_histogram}.py``.
+Each recovers ``accum_logp`` bit-for-bit at its identity knob.  Reference counterparts:
+``jetspec/tree/baselines/accum_logp.py:43-91`` (``AccumLogP``),
+``jetspec/tree/tree_to_chain/fanout_cap/top2gap.py:36-114`` (``Top2GapFanout``, sigmoid cap ``:101``),
+``jetspec/tree/profile_guided/depth_rank_histogram.py:39-107`` (``DepthRankHistogram``),
+``jetspec/tree/semantic_aware/task_router.py:71-180`` (``PromptTaskClassifier``),
+``jetspec/tree/semantic_aware/reasoning_router.py:64-185`` (``ReasoningModeDetector``),
+``jetspec/tree/semantic_aware/class_histogram.py:66-224`` (``ClassifierPerClassHistogram``).
 """
 from __future__ import annotations
 

@@ -2,7 +2,8 @@
 
 ``anc[i, j]`` is true when node ``j`` lies on the path root → ``i`` (``i`` itself
 included).  Because parents precede children, one forward sweep that ORs each
-row with its parent's row suffices.
+row with its parent's row suffices.  Reference counterpart: ``jetspec/tree/_core/ancestor.py:19-55`` (bool and
+uint8-packed matrices); the int32 bit words the attention kernels read are this framework's own.
 """
 from __future__ import annotations
 

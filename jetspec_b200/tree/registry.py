@@ -1,4 +1,5 @@
-"""Name → algorithm registry (``register_tree_algo`` / ``get_algorithm`` / ``list_algorithms``)."""
+"""Name → algorithm registry (``register_tree_algo`` / ``get_algorithm`` / ``list_algorithms``), the public
+contract of ``jetspec/tree/_core/registry.py:18-39``."""
 from __future__ import annotations
 
 from .types import TreeAlgorithm
