@@ -1,4 +1,6 @@
 // Paged tree-masked attention on the 5th-generation tensor cores (tcgen05 + tensor memory), head_dim 128.
+// Reference twins: the Triton paged kernel jetspec/inference_engine/paged_tree_attn.py:55-367 (fp32 qq_bias, block tables)
+// and the dense tree-attention kernel of the Hugging Face path, jetspec/core/tree_attention_kernel.py:63-216.
 //
 // Same contract as the mma.sync kernel in attn_sm100.cu (logical positions through a slot map, packed
 // ancestor bits or causal window, GQA group packed into rows, optional key splits merged by

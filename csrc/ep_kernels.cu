@@ -1,4 +1,5 @@
 // Expert-parallel dispatch for sparse-MoE layers whose tokens are SHARDED over the ranks.
+// (The reference's MoE is single-GPU, jetspec/models/moe_fused.py:16-116; this exchange has no counterpart there.)
 //
 // Every rank owns some tokens (its requests' tree nodes) and some experts (E / world consecutive ones).  A
 // layer moves each (token, choice) row to the rank that owns the chosen expert, runs the experts there as

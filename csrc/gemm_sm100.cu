@@ -1,4 +1,6 @@
 // bf16 GEMM for sm_100a:  C[M,N] = A[M,K] * W[N,K]^T  with fused epilogues.
+// Reference twins (library GEMMs + ATen glue of the fused verify stack): jetspec/inference_engine/compiled_verify_stack.py:170-272
+// (fused QKV, o_proj, gate/up + activation, down + residual, LM head); grouped mode: jetspec/models/moe_fused.py:16-116.
 //
 // Both operands are K-major (activations row-major, weights in nn.Linear layout), so a tile
 // is a stack of 128-byte rows that TMA drops into shared memory with the 128-byte swizzle and

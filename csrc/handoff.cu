@@ -1,4 +1,5 @@
 // Target <-> draft-GPU handoff primitives (the draft head lives on its own GPU).
+// (The reference keeps the head on the target's device, jetspec/draft_head_adapter.py:54,73,129; no counterpart there.)
 //
 // The target's tapped hidden rows are written into the drafter GPU's buffer directly by the
 // layer-epilogue copy kernel (its destination is simply a peer address).  What remains is small

@@ -1,4 +1,6 @@
 // Memory-bound helper kernels of the decode round: embedding gather, RMSNorm, the fused
+// Reference twins: the ATen ops between the GEMMs of jetspec/inference_engine/compiled_verify_stack.py:170-272 (norms, RoPE,
+// KV write) and the drafter's log_softmax + topk, jetspec/tree/_core/topk_build.py:10-63 / jetspec/draft_head_adapter.py:129.
 // QKV post-processing (per-head RMSNorm + RoPE + KV scatter into slots), SwiGLU, row
 // gathers, and the merges of the per-tile argmax / top-k partials the LM-head GEMM emits.
 // All math is fp32; tensors are bf16.  Each kernel joins programmatic dependent launch:

@@ -1,4 +1,5 @@
 // Small tensor-parallel collectives done with peer stores inside the kernel.
+// (No counterpart in the reference: its only collectives are the benchmark's NCCL reductions, bench/engine/tps_walltime.py:111-139.)
 //
 // tp_argmax_combine: the LM head is sharded over the vocabulary; each rank has merged its own
 // tiles into a per-row (value, token) pair.  Every rank stores its pairs into every rank's
